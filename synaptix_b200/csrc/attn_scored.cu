@@ -1,0 +1,457 @@
+// Attention whose weights are a function of ALL heads' scores of a (query, key) pair, over the paged cache, in 32-bit
+// FFMA (scores, their mixture over heads, the weights and the weighted sums of values never leave 32-bit):
+//
+//   s_g(i, j)  = (q_g(i) . k_kv(g)(j)) * scale                       for every query head g
+//   s'_h(i, j) = sum_g talk[h, g] s_g(i, j)                          (talk null: s'_h = s_h)
+//              + head_bias[h] + dist_bias[h, min(i - j, dist_n - 1)] (each null: not added)
+//   weight     = sigmoid(s'_h)  (not normalised over keys)   or   softmax over the visible keys
+//   o_h(i)     = sum_j weight_h(i, j) v_kv(h)(j)  [* gate[i, h]]
+//
+// Key j is visible to the query at position i iff j <= i and (window == 0 or j > i - window).
+//
+// heads_prepare_kernel makes q, k, v out of a float32 projection row [q heads | k heads | v heads | gates]: bias,
+// optional RMS norm of every q and k head with a gain shared by the heads, optional rotation of NEIGHBOURING pairs
+// (2i, 2i + 1) of the first rot_dims elements by position * inv_freq[i] with cos and sin times `mag`, optional blend of
+// the values with those another layer made for the same token (v <- (1 - lam) v + lam v_first), cache write, and
+// sigmoid of the gate columns.
+#include "common.cuh"
+
+__device__ __forceinline__ float sigmoid_acc(float x) { return 1.f / (1.f + expf(-x)); }
+
+// ---------------------------------------------------------------------------------------
+// head preparation: one block a token, a warp a head at a time
+// ---------------------------------------------------------------------------------------
+struct PrepArgs {
+  const float* proj; int row; const float* bias;
+  void* q_out; void* k_pages; void* v_pages;
+  const int* positions; const int* seq_of_token; const int* block_table; int maxp; int n_pages;
+  int H, G, dim, vdim;
+  const float* qn; const float* kn; float eps;
+  const float* inv_freq; int rot_dims; float mag;
+  const float* v_first_in; float* v_first_out; const float* lam;
+  float* gate_out; int n_gate;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) heads_prepare_kernel(const PrepArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = a.positions[t];
+  const float* src_tok = a.proj + (size_t)t * a.row;
+  const int s = a.seq_of_token[t];
+  const int page = a.block_table[(size_t)s * a.maxp + (pos >> 6)];
+  const bool page_ok = page >= 0 && page < a.n_pages;
+  const int H = a.H, G = a.G, dim = a.dim, vdim = a.vdim;
+  const int half = a.inv_freq ? a.rot_dims / 2 : 0;
+  const float lam = (a.v_first_in && a.lam) ? *a.lam : 0.f;
+
+  for (int head = warp; head < H + 2 * G; head += 4) {
+    const bool is_q = head < H, is_k = !is_q && head < H + G;
+    if (is_q || is_k) {
+      const int col = head * dim;
+      const float* src = src_tok + col;
+      const float* bs = a.bias ? a.bias + col : nullptr;
+      const float* gain = is_q ? a.qn : a.kn;
+      T* dst;
+      if (is_q) {
+        dst = (T*)a.q_out + ((size_t)t * H + head) * dim;
+      } else {
+        if (!a.k_pages || !page_ok) continue;
+        dst = (T*)a.k_pages + (((size_t)page * G + (head - H)) * SX_PAGE + (pos & 63)) * dim;
+      }
+      float inv = 1.f;
+      if (gain) {
+        float ss = 0.f;
+        for (int d = lane; d < dim; d += 32) { const float x = src[d] + (bs ? bs[d] : 0.f); ss += x * x; }
+        inv = rsqrtf(warp_sum(ss) / (float)dim + a.eps);
+      }
+      for (int i = lane; i < half; i += 32) {
+        float u = src[2 * i] + (bs ? bs[2 * i] : 0.f), v = src[2 * i + 1] + (bs ? bs[2 * i + 1] : 0.f);
+        if (gain) { u *= inv * gain[2 * i]; v *= inv * gain[2 * i + 1]; }
+        float sn, cs;
+        sincosf((float)pos * a.inv_freq[i], &sn, &cs);
+        sn *= a.mag; cs *= a.mag;
+        dst[2 * i] = from_f32<T>(u * cs - v * sn);
+        dst[2 * i + 1] = from_f32<T>(v * cs + u * sn);
+      }
+      for (int d = 2 * half + lane; d < dim; d += 32) {
+        float x = src[d] + (bs ? bs[d] : 0.f);
+        if (gain) x *= inv * gain[d];
+        dst[d] = from_f32<T>(x);
+      }
+    } else {
+      const int c = head - H - G;
+      const int col = (H + G) * dim + c * vdim;
+      const float* src = src_tok + col;
+      T* dst = (a.v_pages && page_ok) ? (T*)a.v_pages + (((size_t)page * G + c) * SX_PAGE + (pos & 63)) * vdim : nullptr;
+      for (int d = lane; d < vdim; d += 32) {
+        float x = src[d] + (a.bias ? a.bias[col + d] : 0.f);
+        const size_t vi = ((size_t)t * G + c) * vdim + d;
+        if (a.v_first_in) x = (1.f - lam) * x + lam * a.v_first_in[vi];
+        if (a.v_first_out) a.v_first_out[vi] = x;
+        if (dst) dst[d] = from_f32<T>(x);
+      }
+    }
+  }
+  if (a.gate_out) {
+    const int col = (H + G) * dim + G * vdim;
+    for (int i = threadIdx.x; i < a.n_gate; i += blockDim.x)
+      a.gate_out[(size_t)t * a.n_gate + i] = sigmoid_acc(src_tok[col + i] + (a.bias ? a.bias[col + i] : 0.f));
+  }
+}
+
+extern "C" int sx_heads_prepare(const float* proj, int row, const float* bias, void* q_out, void* k_pages, void* v_pages,
+                                const int* positions, const int* seq_of_token, const int* block_table, int maxp, int n_pages,
+                                int n_tokens, int H, int G, int dim, int vdim, const float* qn, const float* kn, float eps,
+                                const float* inv_freq, int rot_dims, float mag, const float* v_first_in, float* v_first_out,
+                                const float* lam, float* gate_out, int n_gate, int dt, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || rot_dims < 0 || rot_dims % 2 || rot_dims > dim ||
+      row < (H + G) * dim + G * vdim + n_gate)
+    return SX_ERR_SIZE;
+  PrepArgs a;
+  a.proj = proj; a.row = row; a.bias = bias; a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages;
+  a.positions = positions; a.seq_of_token = seq_of_token; a.block_table = block_table; a.maxp = maxp; a.n_pages = n_pages;
+  a.H = H; a.G = G; a.dim = dim; a.vdim = vdim; a.qn = qn; a.kn = kn; a.eps = eps; a.inv_freq = inv_freq;
+  a.rot_dims = rot_dims; a.mag = mag; a.v_first_in = v_first_in; a.v_first_out = v_first_out; a.lam = lam;
+  a.gate_out = gate_out; a.n_gate = n_gate;
+  if (dt == SX_F32) return sx_launch(heads_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, a);
+  if (dt == SX_BF16) return sx_launch(heads_prepare_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, a);
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
+// the attention
+// ---------------------------------------------------------------------------------------
+#define SC_THREADS 256
+#define SC_KT 32                 // keys a tile: a lane a key where a warp works on one head
+
+struct ScArgs {
+  const void* q; const void* k_pages; const void* v_pages; void* out; float* part; float* part_ml;
+  const int* positions; const int* seq_of_token; const int* block_table; int maxp;
+  const int* tile_tok0; const int* tile_rows;
+  int H, G, dim, vdim; float scale; int window;
+  const float* talk; const float* head_bias; const float* dist_bias; int dist_n;
+  int softmax; int n_chunks; int out_stride; const float* gate;
+};
+
+template <typename T> struct sc_io;
+template <> struct sc_io<bf16> {
+  static constexpr int KV = 8;        // elements of a 16-byte load
+  static __device__ __forceinline__ void ld16(const bf16* p, float* f) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 x = __bfloat1622float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+  }
+  static __device__ __forceinline__ void ld4(const bf16* p, float* f) {      // four elements
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    const float2 x = __bfloat1622float2(h[0]), y = __bfloat1622float2(h[1]);
+    f[0] = x.x; f[1] = x.y; f[2] = y.x; f[3] = y.y;
+  }
+};
+template <> struct sc_io<float> {
+  static constexpr int KV = 4;
+  static __device__ __forceinline__ void ld16(const float* p, float* f) {
+    const float4 u = *reinterpret_cast<const float4*>(p);
+    f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+  }
+  static __device__ __forceinline__ void ld4(const float* p, float* f) { ld16(p, f); }
+};
+
+// R: query heads of one item (they share a kv head); TQ: queries a block (consecutive rows of one sequence)
+template <typename T, int R, int TQ>
+__global__ void __launch_bounds__(SC_THREADS) attn_scored_kernel(const ScArgs a) {
+  extern __shared__ __align__(16) unsigned char sc_smem[];
+  pdl_wait();
+  pdl_trigger();
+  constexpr int KV = sc_io<T>::KV;
+  const int H = a.H, G = a.G, dim = a.dim, vdim = a.vdim;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tok0 = a.tile_tok0 ? a.tile_tok0[blockIdx.x] : blockIdx.x;
+  const int rows = a.tile_tok0 ? min(TQ, a.tile_rows[blockIdx.x]) : 1;
+  const int chunk = blockIdx.y;
+
+  // shared memory: q [TQ][H][dim] as stored, S and P [TQ][H][32] float, talk [H][H], corr / m / l [TQ][H]
+  const int qbytes = (TQ * H * dim * (int)sizeof(T) + 15) & ~15;
+  T* qs = reinterpret_cast<T*>(sc_smem);
+  float* S = reinterpret_cast<float*>(sc_smem + qbytes);
+  float* P = S + TQ * H * SC_KT;
+  float* talk = P + TQ * H * SC_KT;
+  float* corr = talk + (a.talk ? H * H : 0);
+  float* mrun = corr + TQ * H;
+  float* lrun = mrun + TQ * H;
+  __shared__ int pos_q[TQ];
+
+  for (int i = tid; i < TQ * H * dim; i += SC_THREADS) {
+    const int tq = i / (H * dim);
+    qs[i] = tq < rows ? reinterpret_cast<const T*>(a.q)[(size_t)(tok0 + tq) * H * dim + (i - tq * H * dim)] : from_f32<T>(0.f);
+  }
+  if (a.talk) for (int i = tid; i < H * H; i += SC_THREADS) talk[i] = a.talk[i];
+  for (int i = tid; i < TQ * H; i += SC_THREADS) { corr[i] = 1.f; mrun[i] = -INFINITY; lrun[i] = 0.f; }
+  if (tid < TQ) pos_q[tid] = tid < rows ? a.positions[tok0 + tid] : -1;
+  __syncthreads();
+
+  const int first_pos = pos_q[0], last_pos = pos_q[rows - 1];
+  const int lo = a.window > 0 ? max(0, first_pos - a.window + 1) : 0;
+  const int* bt = a.block_table + (size_t)a.seq_of_token[tok0] * a.maxp;
+  const int tile_lo = lo >> 5, n_tiles = (last_pos >> 5) - tile_lo + 1;
+  const int per = (n_tiles + a.n_chunks - 1) / a.n_chunks;
+  const int tile_a = tile_lo + chunk * per, tile_b = min(tile_lo + n_tiles, tile_a + per);
+
+  // what this thread accumulates: heads hg*R .. hg*R+R-1, value elements d0 .. d0+3
+  const int nd = (vdim + 3) >> 2;
+  const int item = blockIdx.z * SC_THREADS + tid;
+  const bool own = item < (H / R) * nd;
+  const int hg3 = own ? item / nd : 0, d0 = own ? (item - hg3 * nd) * 4 : 0;
+  const int c3 = (hg3 * R) / (H / G);
+  const bool vvec = (vdim & 3) == 0 && (((uintptr_t)a.v_pages) & 15) == 0;
+  const bool kvec = dim % KV == 0 && (((uintptr_t)a.k_pages) & 15) == 0;
+  float acc[TQ][R][4];
+#pragma unroll
+  for (int tq = 0; tq < TQ; ++tq)
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[tq][r][0] = acc[tq][r][1] = acc[tq][r][2] = acc[tq][r][3] = 0.f;
+
+  const T* kp = reinterpret_cast<const T*>(a.k_pages);
+  const T* vp = reinterpret_cast<const T*>(a.v_pages);
+  for (int tile = tile_a; tile < tile_b; ++tile) {
+    const int j0 = tile << 5;
+    const int page = bt[j0 >> 6];
+    const int prow = j0 & 63;
+    // 1: raw scores of every head, a thread a (group of R heads, key)
+    for (int it = tid; it < (H / R) * SC_KT; it += SC_THREADS) {
+      const int hg = it >> 5, j = it & 31;
+      const int c = (hg * R) / (H / G);
+      float s[TQ][R];
+#pragma unroll
+      for (int tq = 0; tq < TQ; ++tq)
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[tq][r] = 0.f;
+      if (j0 + j <= last_pos) {
+        const T* kr = kp + (((size_t)page * G + c) * SX_PAGE + prow + j) * dim;
+        if (kvec) {
+          for (int d = 0; d < dim; d += KV) {
+            float kf[KV];
+            sc_io<T>::ld16(kr + d, kf);
+#pragma unroll
+            for (int tq = 0; tq < TQ; ++tq)
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                float qf[KV];
+                sc_io<T>::ld16(qs + (size_t)(tq * H + hg * R + r) * dim + d, qf);
+#pragma unroll
+                for (int e = 0; e < KV; ++e) s[tq][r] = fmaf(qf[e], kf[e], s[tq][r]);
+              }
+          }
+        } else {
+          for (int d = 0; d < dim; ++d) {
+            const float kf = to_f32(kr[d]);
+#pragma unroll
+            for (int tq = 0; tq < TQ; ++tq)
+#pragma unroll
+              for (int r = 0; r < R; ++r) s[tq][r] = fmaf(to_f32(qs[(size_t)(tq * H + hg * R + r) * dim + d]), kf, s[tq][r]);
+          }
+        }
+      }
+#pragma unroll
+      for (int tq = 0; tq < TQ; ++tq)
+#pragma unroll
+        for (int r = 0; r < R; ++r) S[(tq * H + hg * R + r) * SC_KT + j] = s[tq][r] * a.scale;
+    }
+    __syncthreads();
+    // 2: mixture over heads, biases, weights: a warp a (query, head), a lane a key
+    for (int p = warp; p < TQ * H; p += SC_THREADS / 32) {
+      const int tq = p / H, h = p - tq * H;
+      const int pq = pos_q[tq], jk = j0 + lane;
+      const bool vis = pq >= 0 && jk <= pq && (a.window == 0 || jk > pq - a.window);
+      float s;
+      if (a.talk) {
+        s = 0.f;
+        const float* tr = talk + h * H;
+        const float* sr = S + tq * H * SC_KT + lane;
+        for (int g = 0; g < H; ++g) s = fmaf(tr[g], sr[g * SC_KT], s);
+      } else {
+        s = S[p * SC_KT + lane];
+      }
+      if (a.head_bias) s += a.head_bias[h];
+      if (a.dist_bias && vis) s += a.dist_bias[(size_t)h * a.dist_n + min(pq - jk, a.dist_n - 1)];
+      float w;
+      if (!a.softmax) {
+        w = vis ? sigmoid_acc(s) : 0.f;
+      } else {
+        s = vis ? s : -INFINITY;
+        const float m_old = mrun[p];
+        const float m_new = fmaxf(m_old, warp_max(s));
+        w = (m_new == -INFINITY) ? 0.f : expf(s - m_new);
+        const float cr = (m_old == -INFINITY) ? 1.f : expf(m_old - m_new);
+        const float ws = warp_sum(w);
+        if (lane == 0) { corr[p] = cr; mrun[p] = m_new; lrun[p] = lrun[p] * cr + ws; }
+      }
+      P[p * SC_KT + lane] = w;
+    }
+    __syncthreads();
+    // 3: weighted sums of the values
+    if (own) {
+      if (a.softmax) {
+#pragma unroll
+        for (int tq = 0; tq < TQ; ++tq)
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const float cr = corr[tq * H + hg3 * R + r];
+            acc[tq][r][0] *= cr; acc[tq][r][1] *= cr; acc[tq][r][2] *= cr; acc[tq][r][3] *= cr;
+          }
+      }
+      const int nj = min(SC_KT, last_pos - j0 + 1);
+      const T* vr0 = vp + (((size_t)page * G + c3) * SX_PAGE + prow) * vdim + d0;
+      for (int j = 0; j < nj; j += 4) {
+        float vf[4][4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          if (j + jj < nj && j0 + j + jj >= lo) {            // keys before the window's edge may lie in memory nobody wrote
+            if (vvec) {
+              sc_io<T>::ld4(vr0 + (size_t)(j + jj) * vdim, vf[jj]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) vf[jj][e] = d0 + e < vdim ? to_f32(vr0[(size_t)(j + jj) * vdim + e]) : 0.f;
+            }
+          } else {
+            vf[jj][0] = vf[jj][1] = vf[jj][2] = vf[jj][3] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int tq = 0; tq < TQ; ++tq)
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const float4 pw = *reinterpret_cast<const float4*>(P + (tq * H + hg3 * R + r) * SC_KT + j);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              acc[tq][r][e] = fmaf(pw.x, vf[0][e], fmaf(pw.y, vf[1][e], fmaf(pw.z, vf[2][e], fmaf(pw.w, vf[3][e], acc[tq][r][e]))));
+          }
+      }
+    }
+    __syncthreads();
+  }
+
+  if (!own) return;
+  if (a.n_chunks == 1) {
+#pragma unroll
+    for (int tq = 0; tq < TQ; ++tq) {
+      if (tq >= rows) continue;
+      T* o = reinterpret_cast<T*>(a.out) + (size_t)(tok0 + tq) * a.out_stride;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int h = hg3 * R + r;
+        float f = 1.f;
+        if (a.softmax) { const float l = lrun[tq * H + h]; f = l > 0.f ? 1.f / l : 0.f; }
+        if (a.gate) f *= a.gate[(size_t)(tok0 + tq) * H + h];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (d0 + e < vdim) o[(size_t)h * vdim + d0 + e] = from_f32<T>(acc[tq][r][e] * f);
+      }
+    }
+    return;
+  }
+  // several chunks of the keys (TQ == 1): unnormalised sums, running maxima and sums of weights for the merge
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int h = hg3 * R + r;
+    float* po = a.part + ((size_t)tok0 * a.n_chunks + chunk) * H * vdim + (size_t)h * vdim;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (d0 + e < vdim) po[d0 + e] = acc[0][r][e];
+    if (a.softmax && d0 == 0) {
+      float* ml = a.part_ml + (((size_t)tok0 * a.n_chunks + chunk) * H + h) * 2;
+      ml[0] = mrun[h];
+      ml[1] = lrun[h];
+    }
+  }
+}
+
+// the chunks of a token's keys added up in chunk order
+template <typename T>
+__global__ void __launch_bounds__(128) attn_scored_merge_kernel(const float* __restrict__ part, const float* __restrict__ part_ml,
+                                                                T* __restrict__ out, const float* __restrict__ gate, int H, int vdim,
+                                                                int n_chunks, int softmax, int out_stride) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H * vdim; i += blockDim.x) {
+    const int h = i / vdim;
+    float m = -INFINITY;
+    if (softmax)
+      for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, part_ml[(((size_t)t * n_chunks + c) * H + h) * 2]);
+    float o = 0.f, l = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+      float f = 1.f;
+      if (softmax) {
+        const float* ml = part_ml + (((size_t)t * n_chunks + c) * H + h) * 2;
+        f = ml[0] == -INFINITY ? 0.f : expf(ml[0] - m);
+        l = fmaf(f, ml[1], l);
+      }
+      o = fmaf(f, part[((size_t)t * n_chunks + c) * H * vdim + i], o);
+    }
+    if (softmax) o = l > 0.f ? o / l : 0.f;
+    if (gate) o *= gate[(size_t)t * H + h];
+    out[(size_t)t * out_stride + i] = from_f32<T>(o);
+  }
+}
+
+template <typename T, int R, int TQ>
+static int scored_launch(const ScArgs& a, int n_tiles, cudaStream_t stream) {
+  const int H = a.H;
+  size_t smem = ((size_t)TQ * H * a.dim * sizeof(T) + 15) & ~(size_t)15;
+  smem += (size_t)(2 * TQ * H * SC_KT + (a.talk ? H * H : 0) + 3 * TQ * H) * sizeof(float);
+  if (smem > 200 * 1024) return SX_ERR_SIZE;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_scored_kernel<T, R, TQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int nd = (a.vdim + 3) / 4;
+  const int items = (H / R) * nd;
+  dim3 grid(n_tiles, a.n_chunks, (items + SC_THREADS - 1) / SC_THREADS);
+  return sx_launch(attn_scored_kernel<T, R, TQ>, grid, dim3(SC_THREADS), smem, stream, a);
+}
+
+template <typename T, int TQ>
+static int scored_pick(const ScArgs& a, int n_tiles, cudaStream_t stream) {
+  const int per = a.H / a.G;
+  if (per % 4 == 0) return scored_launch<T, 4, TQ>(a, n_tiles, stream);
+  if (per % 2 == 0) return scored_launch<T, 2, TQ>(a, n_tiles, stream);
+  return scored_launch<T, 1, TQ>(a, n_tiles, stream);
+}
+
+// tile_tok0 / tile_rows null: a tile is one token (n_tiles = tokens) and the keys may be cut into n_chunks parts
+// (part: float32 [tokens, n_chunks, H, vdim]; part_ml: float32 [tokens, n_chunks, H, 2], softmax only).
+// Otherwise a tile is up to `tq` (1 or 4) consecutive rows of one sequence and n_chunks must be 1.
+extern "C" int sx_attn_scored(const void* q, const void* k_pages, const void* v_pages, void* out, float* part, float* part_ml,
+                              const int* positions, const int* seq_of_token, const int* block_table, int maxp,
+                              const int* tile_tok0, const int* tile_rows, int n_tiles, int tq, int n_tokens, int H, int G, int dim,
+                              int vdim, float scale, int window, const float* talk, const float* head_bias,
+                              const float* dist_bias, int dist_n, int softmax, int n_chunks, int out_stride, const float* gate,
+                              int dt, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || out_stride < H * vdim || n_chunks < 1 || H > 256) return SX_ERR_SIZE;
+  if ((tq != 1 && tq != 4) || (tile_tok0 == nullptr && tq != 1) || (n_chunks > 1 && (tq != 1 || tile_tok0 || !part)))
+    return SX_ERR_SIZE;
+  if (n_chunks > 1 && softmax && !part_ml) return SX_ERR_SIZE;
+  if (dist_bias && dist_n <= 0) return SX_ERR_SIZE;
+  ScArgs a;
+  a.q = q; a.k_pages = k_pages; a.v_pages = v_pages; a.out = out; a.part = part; a.part_ml = part_ml;
+  a.positions = positions; a.seq_of_token = seq_of_token; a.block_table = block_table; a.maxp = maxp;
+  a.tile_tok0 = tile_tok0; a.tile_rows = tile_rows; a.H = H; a.G = G; a.dim = dim; a.vdim = vdim; a.scale = scale;
+  a.window = window; a.talk = talk; a.head_bias = head_bias; a.dist_bias = dist_bias; a.dist_n = dist_n;
+  a.softmax = softmax; a.n_chunks = n_chunks; a.out_stride = out_stride; a.gate = n_chunks == 1 ? gate : nullptr;
+  int rc;
+  if (dt == SX_F32) rc = tq == 4 ? scored_pick<float, 4>(a, n_tiles, stream) : scored_pick<float, 1>(a, n_tiles, stream);
+  else if (dt == SX_BF16) rc = tq == 4 ? scored_pick<bf16, 4>(a, n_tiles, stream) : scored_pick<bf16, 1>(a, n_tiles, stream);
+  else return SX_ERR_DTYPE;
+  if (rc != 0 || n_chunks == 1) return rc;
+  if (dt == SX_F32)
+    return sx_launch(attn_scored_merge_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)part,
+                     (const float*)part_ml, (float*)out, gate, H, vdim, n_chunks, softmax, out_stride);
+  return sx_launch(attn_scored_merge_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, (const float*)part,
+                   (const float*)part_ml, (bf16*)out, gate, H, vdim, n_chunks, softmax, out_stride);
+}

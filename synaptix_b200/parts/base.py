@@ -146,7 +146,33 @@ class PendingLinear:
 
 def plain(t):
     """``t`` as a tensor, whatever deferred form it came in."""
-    return t.materialize() if isinstance(t, (PendingLinear, PendingNorm, ScaledRows, ScaledSum)) else t
+    return t.materialize() if isinstance(t, (PendingLinear, PendingNorm, ScaledRows, ScaledSum, NormedDelta)) else t
+
+
+class NormedDelta:
+    """A branch output that goes through a norm of its own before it is added into the residual stream:
+    ``mult * norm(x + bias)`` with ``x [T, width]`` (compute dtype or float32), ``norm`` a norm with ``weight`` and
+    ``bias`` vectors (a layer norm) and ``bias`` an optional float32 vector over the width (the bias of the branch's
+    last product).  A block whose sublayers are normed on both sides hands this on, and a norm that says
+    ``takes_normed_delta`` forms branch norm, sum and its own norm in one kernel.  ``materialize()`` gives
+    ``mult * norm(x + bias)`` as one float32 tensor."""
+    __slots__ = ("x", "norm", "mult", "bias", "_sum")
+
+    def __init__(self, x, norm, mult: float = 1.0, bias=None):
+        self.x, self.norm, self.mult, self.bias = x, norm, float(mult), bias
+        self._sum = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    def materialize(self) -> torch.Tensor:
+        if self._sum is None:
+            from .. import ops
+            zero = torch.zeros(self.x.shape, dtype=torch.float32, device=self.x.device)
+            _, self._sum = ops.add_layernorm(zero, self.x, self.norm.weight, self.norm.bias, self.norm.eps, torch.float32,
+                                             post=(self.norm.weight, self.norm.bias), mult=self.mult, delta_bias=self.bias)
+        return self._sum
 
 
 class ScaledSum:
@@ -237,6 +263,7 @@ class Part:
 class Norm(Part):
     takes_pending_product = False  # True: add_forward may be handed a PendingLinear as delta
     takes_scaled_sum = False       # True: add_forward may be handed a ScaledSum as delta
+    takes_normed_delta = False     # True: add_forward may be handed a NormedDelta as delta
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

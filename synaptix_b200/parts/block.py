@@ -16,6 +16,9 @@ norm of its own and times a learned vector over the width (a layer scale):
 ``h += mult * (ls1 * mixer(norm1(h)) + ls2 * ffn(norm2(h)))``.  Both norms share the
 row's root mean square, so one kernel makes both; the sum is handed on as a
 ``ScaledSum`` and added by the next norm's kernel.  The feed-forward half may be absent.
+
+``SandwichBlock``: every sublayer between two norms, ``h += mult * post(sublayer(pre(h)))``,
+with an optional ``TokenShift`` of what the mixer reads.
 """
 from __future__ import annotations
 
@@ -26,7 +29,7 @@ import torch
 from .. import ops
 from ..cache.store import BundleRequest, StateRequest
 from ..weights.loader import TensorSpec
-from .base import (FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, Runtime, ScaledRows, ScaledSum,
+from .base import (FeedForward, Mixer, Norm, NormedDelta, Part, PendingLinear, PendingNorm, Runtime, ScaledRows, ScaledSum,
                    StepContext, plain, to_device_f32)
 
 
@@ -195,3 +198,69 @@ class ParallelBlock(Part):
             a = self.mixer.forward(xs[0], ctx, cache_view, write_cache)
             b = self.ffn.forward(xs[1], ctx)
         return h, ScaledSum([(a, self.s1), (b, self.s2)])
+
+
+class TokenShift(Part):
+    """What a sublayer reads is blended with what it read for the token before: ``y_t + (y_(t-1) - y_t) * s`` with a
+    learned vector ``s`` over the width and ``y_(-1) = 0``.  The last ``y`` of a sequence is part of its state."""
+
+    def __init__(self, weight_name: str, width: int):
+        self.weight_name, self.width = weight_name, width
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.weight_name: TensorSpec((self.width,), "bias")}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.weight = to_device_f32(tensors[self.weight_name], rt)
+
+    def state_request(self) -> StateRequest:
+        return StateRequest((self.width,), torch.float32)
+
+
+class SandwichBlock(Part):
+    """Sublayers normed on both sides: ``h += mult * post1(mixer(shift(pre1(h))))``, then
+    ``h += mult * post2(ffn(pre2(h)))``.  The four norms take ``NormedDelta`` (layer norms); ``shift`` (a
+    ``TokenShift``, optional) blends the mixer's input with the previous token's; ``pre2, post2, ffn`` may all be
+    ``None``.  A branch's output travels on as a ``NormedDelta`` so that its own norm, the sum into the stream and the
+    next norm are one kernel.  ``mixer.output_bias`` (a float32 vector or ``None``), when the mixer has one, is the
+    bias of its last product, added inside that kernel.  Cache entry: the mixer's request, or the bundle (mixer's
+    request, the shift's last input)."""
+    takes_pending_product = False
+
+    def __init__(self, pre1: Norm, mixer: Mixer, post1: Norm, pre2: Optional[Norm] = None, ffn: Optional[FeedForward] = None,
+                 post2: Optional[Norm] = None, *, mult: float = 1.0, shift: Optional[TokenShift] = None):
+        if (pre2 is None) != (ffn is None) or (post2 is None) != (ffn is None):
+            raise ValueError("pre2, ffn and post2 come together or not at all")
+        for n in (pre1, post1, pre2, post2):
+            if n is not None and not n.takes_normed_delta:
+                raise ValueError("the norms of a sandwich block take a branch with a norm of its own")
+        self.pre1, self.mixer, self.post1 = pre1, mixer, post1
+        self.pre2, self.ffn, self.post2 = pre2, ffn, post2
+        self.mult = float(mult)
+        self.shift = shift
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.pre1, self.shift, self.mixer, self.post1, self.pre2, self.ffn, self.post2) if p is not None]
+
+    def cache_request(self):
+        if self.shift is None:
+            return self.mixer.cache_request()
+        return BundleRequest((self.mixer.cache_request(), self.shift.state_request()))
+
+    def forward(self, h: torch.Tensor, pending, ctx: StepContext, views, write_cache: bool = True):
+        if self.shift is not None:
+            mixer_view, shift_state = views
+            # a block reads its neighbour's row of the stream before the sum, so the sums go to a new tensor unless
+            # every sequence brings one row
+            x, h = self.pre1.add_forward(h, pending, shift=self.shift.weight, state=shift_state, ctx=ctx,
+                                         in_place=bool(ctx.all_single))
+        else:
+            mixer_view = views
+            x = self.pre1.add_forward(h, pending)
+        a = self.mixer.forward(x, ctx, mixer_view, write_cache)
+        a = NormedDelta(a, self.post1, self.mult, getattr(self.mixer, "output_bias", None))
+        if self.ffn is None:
+            return h, a
+        y = self.pre2.add_forward(h, a)
+        return h, NormedDelta(self.ffn.forward(y, ctx), self.post2, self.mult)

@@ -27,11 +27,13 @@ class SwiGLU(FeedForward):
     accepts_lazy_input = True      # x goes straight into the fused gate/up product
     can_defer_output = True        # the down projection may be handed on unrun
 
-    def __init__(self, prefix: str, width: int, intermediate: int):
+    NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+    def __init__(self, prefix: str, width: int, intermediate: int, names: Optional[Mapping[str, str]] = None):
         self.width, self.intermediate = width, intermediate
-        self.gate_up = Linear([prefix + "gate_proj.weight", prefix + "up_proj.weight"], width,
-                              [intermediate, intermediate])
-        self.down = Linear(prefix + "down_proj.weight", intermediate, width)
+        n = dict(self.NAMES, **(names or {}))
+        self.gate_up = Linear([prefix + n["gate"], prefix + n["up"]], width, [intermediate, intermediate])
+        self.down = Linear(prefix + n["down"], intermediate, width)
 
     def children(self) -> List[Part]:
         return [self.gate_up, self.down]

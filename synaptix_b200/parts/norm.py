@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Norm, PendingLinear, PendingNorm, Runtime, ScaledRows, ScaledSum, to_device_f32
+from .base import Norm, NormedDelta, PendingLinear, PendingNorm, Runtime, ScaledRows, ScaledSum, plain, to_device_f32
 
 
 class RMSNorm(Norm):
@@ -59,3 +59,45 @@ class RMSNorm(Norm):
         if lazy and rows is None and ops.norm_fusable(h.shape[0], h.shape[1], self._dtype):
             return PendingNorm(h, delta, self.weight, self.eps, self._dtype)
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self._dtype, rows=rows)
+
+
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w + b`` over the width, ``var`` the mean of the squared deviations, all in
+    32-bit; ``bias_name`` defaults to the gain's name with ``.b`` added.  Fused with the sum into the residual stream,
+    also of a branch that has a norm of its own (``NormedDelta``)."""
+    takes_normed_delta = True
+
+    def __init__(self, weight_name: str, width: int, eps: float, bias_name: Optional[str] = None):
+        self.weight_name = weight_name
+        self.bias_name = bias_name if bias_name is not None else weight_name + ".b"
+        self.width = width
+        self.eps = float(eps)
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self._dtype = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.weight_name: TensorSpec((self.width,), "gain"), self.bias_name: TensorSpec((self.width,), "bias")}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.weight = to_device_f32(tensors[self.weight_name], rt)
+        self.bias = to_device_f32(tensors[self.bias_name], rt)
+        self._dtype = rt.dtype
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return ops.add_layernorm(h, None, self.weight, self.bias, self.eps, self._dtype)[0]
+
+    def add_forward(self, h, delta, rows=None, lazy=False, shift=None, state=None, ctx=None, in_place=True):
+        """``shift``, ``state``, ``ctx``: a token shift of the normed rows (see ``ops.add_layernorm``); the stream
+        after the sum is then returned too: ``(y, h')``."""
+        kw = {}
+        if isinstance(delta, NormedDelta):
+            kw = dict(post=(delta.norm.weight, delta.norm.bias), mult=delta.mult, delta_bias=delta.bias)
+            if delta.norm.eps != self.eps:
+                raise ValueError("a branch's norm and the norm behind the sum share their eps")
+            delta = delta.x
+        else:
+            delta = plain(delta)
+        y, h_after = ops.add_layernorm(h, delta, self.weight, self.bias, self.eps, self._dtype, rows=rows, shift=shift,
+                                       state=state, ctx=ctx, in_place=in_place, **kw)
+        return (y, h_after) if shift is not None else y

@@ -13,6 +13,9 @@ capacity and no rounding of the table.
 """
 from __future__ import annotations
 
+import math
+from typing import NamedTuple
+
 import numpy as np
 import torch
 
@@ -58,14 +61,44 @@ class RotaryPairs(RotaryHalf):
     rotate ask ``pairs``: ``True`` here, ``False`` for the rotate-half layout."""
     pairs = True
 
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, scaling: "FrequencyRamp" = None):
+        super().__init__(head_dim, theta, rotary_dim)
+        self.scaling = scaling
+        self.magnitude = 1.0 if scaling is None else scaling.magnitude()
+
     def bind(self, tensors, rt: Runtime) -> None:
         # frequencies to the nearest 32-bit value (formed in 64-bit, rounded once)
-        key = ("pairs", self.theta, self.rotary_dim, str(rt.device))
+        key = ("pairs", self.theta, self.rotary_dim, self.scaling, str(rt.device))
         if key not in _INV_FREQ:
             i = np.arange(self.rotary_dim // 2, dtype=np.float64)
-            f = np.power(np.float64(self.theta), -2.0 * i / self.rotary_dim).astype(np.float32)
-            _INV_FREQ[key] = torch.from_numpy(f).to(rt.device)
+            f = np.power(np.float64(self.theta), -2.0 * i / self.rotary_dim)
+            if self.scaling is not None:
+                f = self.scaling.apply(f, self.theta, self.rotary_dim)
+            _INV_FREQ[key] = torch.from_numpy(f.astype(np.float32)).to(rt.device)
         self.inv_freq = _INV_FREQ[key]
+
+
+class FrequencyRamp(NamedTuple):
+    """Context extension by stretching the slow frequencies (the YaRN scheme): with ``dim(t) = dims ln(original /
+    (2 pi t)) / (2 ln base)``, ``lo = max(floor(dim(fast)), 0)``, ``hi = min(ceil(dim(slow)), dims - 1)`` and
+    ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, pair ``i`` turns at ``f_i / factor * ramp_i + f_i (1 -
+    ramp_i)``, and cos and sin are both multiplied by ``0.1 ln(factor) + 1``."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+    def magnitude(self) -> float:
+        return 0.1 * math.log(self.factor) + 1.0
+
+    def apply(self, f: np.ndarray, base: float, dims: int) -> np.ndarray:
+        def dim_of(t):
+            return dims * math.log(self.original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+        lo = max(math.floor(dim_of(self.fast)), 0)
+        hi = min(math.ceil(dim_of(self.slow)), dims - 1)
+        i = np.arange(f.shape[0], dtype=np.float64)
+        ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / self.factor * ramp + f * (1.0 - ramp)
 
 
 class NoPosition(PositionEncoding):

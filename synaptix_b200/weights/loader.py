@@ -27,7 +27,8 @@ class TensorSpec(NamedTuple):
 
     ``kind`` steers the random-weights mode only: ``matrix`` and ``embedding``
     are zero-mean normal, ``gain`` is one plus normal, ``table`` is an integer
-    table (filled with zeros).
+    table (filled with zeros).  A size of ``-1`` in ``shape`` is read from the tensor
+    (random weights need every size).
     """
     shape: Tuple[int, ...]
     kind: str = "matrix"
@@ -122,8 +123,10 @@ def check_tensors(specs: Mapping[str, TensorSpec], shapes: Mapping[str, Tuple[in
     """Raise one ``WeightError`` naming everything that does not fit, or return."""
     missing = sorted(n for n, s in specs.items() if n not in shapes and not s.optional)
     unexpected = sorted(n for n in shapes if n not in specs)
+    def fits(got, want):          # -1 in a spec: the tensor itself says that size
+        return len(got) == len(want) and all(w == -1 and g > 0 or g == w for g, w in zip(got, want))
     wrong = sorted((n, tuple(shapes[n]), tuple(s.shape)) for n, s in specs.items()
-                   if n in shapes and tuple(shapes[n]) != tuple(s.shape))
+                   if n in shapes and not fits(tuple(shapes[n]), tuple(s.shape)))
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, where=where)
 
