@@ -190,10 +190,10 @@ class LedudraConfig(ModelConfig):
         for i, layer in enumerate(self.layers):
             layer.validate(i)
             if layer.mixer.v_mix:
-                size = layer.mixer.kv_heads * layer.mixer.vdim
+                size = (layer.mixer.kv_heads, layer.mixer.vdim)
                 if shared is not None and size != shared:
-                    raise ConfigError(f"config.json: layers[{i}] blends its values with the first v_mix layer's, "
-                                      f"which have {shared} elements a token, not {size}")
+                    raise ConfigError(f"config.json: layers[{i}] blends its values with the first v_mix layer's, which "
+                                      f"has {shared[0]} kv heads of {shared[1]}, not {size[0]} of {size[1]}")
                 shared = size
 
     def first_value_layer(self) -> Optional[int]:
