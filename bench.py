@@ -264,9 +264,21 @@ def pidutar_config(width, ff, nh, nkv, hd, rh, runs, vocab):
                 residual_mult=0.5, logit_scale=1.0, layers=layers)
 
 
+def ledudra_config(width, ff, nh, nkv, hd, rh, runs, vocab):
+    """``runs`` layers, (attention_2, attention) in turn: grouped heads of ``hd`` for keys and values, windows of 1,000,
+    values blended with the first layer's, half of a head rotated with stretched frequencies in the sigmoid layers, a
+    distance table of 32 buckets up to 512 in the softmax layers, SwiGLU of ``ff`` everywhere."""
+    common = dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, scale=hd ** -0.5, mask=dict(size=1000), v_mix=True)
+    soft = dict(type="attention_2", mixer=dict(common, bias_max=512, bias_rows=32), mlp=dict(kind="dense", ff=ff))
+    sigm = dict(type="attention", mixer=dict(common, rot=dict(dims=hd // 2, base=1.0e6, scaling=dict(
+        factor=8.0, original=1024, fast=32.0, slow=1.0))), mlp=dict(kind="dense", ff=ff))
+    return dict(architecture="Ledudra", vocab=vocab, width=width, norm=dict(eps=1e-5), residual_mult=0.5,
+                layers=[(soft if i % 2 == 0 else sigm) for i in range(runs)])
+
+
 def arch_points(torch, a):
     from synaptix_b200.api import LLM
-    from synaptix_b200.config import PidutarConfig, Qwen3Config, VemedraConfig
+    from synaptix_b200.config import LedudraConfig, PidutarConfig, Qwen3Config, VemedraConfig
     from synaptix_b200.engine import DecodeRow, Entry
     from synaptix_b200.models import model_skeleton
     from synaptix_b200.parts import Runtime
@@ -327,12 +339,15 @@ def arch_points(torch, a):
         width, ff, nh, nkv, hd, rh = VEMEDRA_SIZES[name]
         if a.arch == "pidutar":
             measure(PidutarConfig.from_dict(pidutar_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"pidutar_{name}")
-        measure(VemedraConfig.from_dict(vemedra_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"vemedra_{name}")
+        if a.arch == "ledudra":
+            measure(LedudraConfig.from_dict(ledudra_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"ledudra_{name}")
+        else:
+            measure(VemedraConfig.from_dict(vemedra_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"vemedra_{name}")
         measure(Qwen3Config.from_dict(dict(QWEN3_4B, num_hidden_layers=RUNS, hidden_size=width, num_attention_heads=nh,
                                            num_key_value_heads=nkv, head_dim=hd, intermediate_size=ff, vocab_size=VOCAB,
                                            tie_word_embeddings=False)), f"qwen3_{name}")
-    return {"metric": f"prompt step and decode step, {'Pidutar beside Vemedra and' if a.arch == 'pidutar' else 'Vemedra beside'} "
-                      "Qwen3 at equal sizes (bf16, random weights)", "impl": "ours",
+    beside = {"pidutar": "Pidutar beside Vemedra and", "vemedra": "Vemedra beside", "ledudra": "Ledudra beside"}[a.arch]
+    return {"metric": f"prompt step and decode step, {beside} Qwen3 at equal sizes (bf16, random weights)", "impl": "ours",
             "layer_runs": RUNS, "vocab": VOCAB, "context": CONTEXT, "steps": K, "warmup": a.warmup, "sizes": VEMEDRA_SIZES,
             "data": "synthetic", "dtype": "bf16", "points": out}
 
@@ -358,10 +373,10 @@ def main():
     ap.add_argument("--short", action="store_true",
                     help="decode only 5 x --steps + --warmup tokens instead of at least 255 (small cases for profilers: "
                          "every launch under a profiler costs a good part of a second)")
-    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "vemedra", "pidutar"],
+    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "vemedra", "pidutar", "ledudra"],
                     help="vemedra: the Vemedra decoder beside Qwen3 at equal sizes (prompt step, decode at batch 1 and 8) instead of "
-                         "the default run; pidutar: the Pidutar decoder beside both")
-    ap.add_argument("--arch-sizes", default="", help="with --arch vemedra or pidutar: which of 1k,2.5k,4k (default: all)")
+                         "the default run; pidutar: the Pidutar decoder beside both; ledudra: the Ledudra decoder beside Qwen3")
+    ap.add_argument("--arch-sizes", default="", help="with --arch vemedra, pidutar or ledudra: which of 1k,2.5k,4k (default: all)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -375,7 +390,7 @@ def main():
     a.warmup = max(a.warmup, 3)
 
     import torch
-    if a.arch in ("vemedra", "pidutar"):
+    if a.arch in ("vemedra", "pidutar", "ledudra"):
         a.steps = min(a.steps, 40)
         print(json.dumps(arch_points(torch, a)))
         return 0

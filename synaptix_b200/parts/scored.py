@@ -115,7 +115,7 @@ class ScoredAttention(Mixer):
         if self.biases:
             cols = [tensors[b].to(torch.float32) for b in self._bias_names]
             if self.head_gate:
-                cols.append(torch.zeros(self.nh, dtype=torch.float32))       # the gate's projection has no bias
+                cols.append(torch.zeros(self.nh, dtype=torch.float32, device=cols[0].device))       # the gate's projection has no bias
             self.proj_bias = to_device_f32(torch.cat(cols), rt)
             self.output_bias = to_device_f32(tensors[p + n["o"] + n["bias_suffix"]], rt)
         if self.qk_norm_eps is not None:
@@ -129,7 +129,7 @@ class ScoredAttention(Mixer):
             # the table as the kernel reads it: [H, distances], the bucket of every distance looked up once
             table = tensors[p + n["distance"]].to(torch.float32)
             cols = distance_columns(table.shape[0], self.distance_bias[1], self.window)
-            table = table[torch.from_numpy(cols)]                                                 # [distances, H]
+            table = table[torch.from_numpy(cols).to(table.device)]                                               # [distances, H]
             self.distance_table = to_device_f32(table.t(), rt)
         if self.value_mix == "blend":
             self.lam = to_device_f32(tensors[p + n["lam"]].reshape(1), rt)
