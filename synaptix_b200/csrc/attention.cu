@@ -163,7 +163,9 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   // the scale that turns the running maxima into the log2 domain (1 when the scores are capped: they are there already)
-  const float sl_m = (EX && ex.cap_log2 > 0.f) ? 1.f : scale_log2;
+  const float sl_m = (EX && (ex.cap_log2 > 0.f || ex.dist)) ? 1.f : scale_log2;
+  const float* dist_lo = (EX && ex.dist) ? ex.dist + (size_t)(kvh * G + min(g, G - 1)) * ex.dist_n : nullptr;
+  const float* dist_hi = (EX && ex.dist) ? ex.dist + (size_t)(kvh * G + min(g + 8, G - 1)) * ex.dist_n : nullptr;
   if (EX && ex.sinks && warp == 0 && split == 0) {            // the sink counts once: in the first warp of the first split
     if (g < G) { m[0] = ex.sinks[kvh * G + g] * 1.4426950408889634f / sl_m; l[0] = t == 0 ? 1.f : 0.f; }
     if (g + 8 < G) { m[1] = ex.sinks[kvh * G + g + 8] * 1.4426950408889634f / sl_m; l[1] = t == 0 ? 1.f : 0.f; }
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     const int jb = (p0 + i) * 64;
     if (EX)
       attend_tile<HD, 2, true, true>(qf, st, st + L::TILE, warp * 16, jb, pos, pos, window, scale_log2, m, l, o, lo, lo,
-                                     ex.cap_log2, ex.cap_in);
+                                     ex.cap_log2, ex.cap_in, dist_lo, dist_hi, ex.dist_n);
     else if (jb + 63 > pos || (window > 0 && jb <= pos - window))
       attend_tile<HD, 2, true>(qf, st, st + L::TILE, warp * 16, jb, pos, pos, window, scale_log2, m, l, o);
     else      // the whole page is visible: no comparisons
@@ -351,7 +353,7 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   if (EX && ex.sinks) {                                       // the sink: a term exp(sink) of the denominator without a key
-    const float s0 = ex.sinks[h] * 1.4426950408889634f / (ex.cap_log2 > 0.f ? 1.f : scale_log2);
+    const float s0 = ex.sinks[h] * 1.4426950408889634f / ((ex.cap_log2 > 0.f || ex.dist) ? 1.f : scale_log2);
     m[0] = m[1] = s0;
     l[0] = l[1] = t == 0 ? 1.f : 0.f;
   }
@@ -370,6 +372,7 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
     warp_low = ((past + q0 + warp * 16) / ex.chunk) * ex.chunk;
     warp_low_last = ((past + q0 + min(rows - 1, warp * 16 + 15)) / ex.chunk) * ex.chunk;
   }
+  const float* dist_row = (EX && ex.dist) ? ex.dist + (size_t)h * ex.dist_n : nullptr;
   const int p0 = lo_key >> 6, p1 = (last_pos >> 6) + 1;
   const int npages = p1 - p0;
   // this warp needs pages up to its own last row only
@@ -397,10 +400,10 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
         // the window) needs no comparisons
         if (jbase + 63 > warp_first || jbase < warp_low_last || (window > 0 && jbase <= warp_last - window))
           attend_tile<HD, 8, true, true>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o, low_lo, low_hi,
-                                         ex.cap_log2, ex.cap_in);
+                                         ex.cap_log2, ex.cap_in, dist_row, dist_row, ex.dist_n);
         else
           attend_tile<HD, 8, false, true>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o, low_lo, low_hi,
-                                          ex.cap_log2, ex.cap_in);
+                                          ex.cap_log2, ex.cap_in, dist_row, dist_row, ex.dist_n);
       }
     } else if (warp_on && jbase <= warp_last) {
       // visible to every row of this warp without a comparison: ends before the warp's first row's
@@ -447,7 +450,7 @@ static int decode_launch(const bf16* q, bf16* k, bf16* v, bf16* out, float* part
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_splits, nkv, S);
-  const AtExtra no_extra = {0.f, 0.f, nullptr, 0, 0, 1.f};
+  const AtExtra no_extra = {0.f, 0.f, nullptr, 0, 0, 1.f, nullptr, 0};
   int rc = sx_launch(kern, grid, dim3(AT_THREADS), smem, stream, q, k, v, out, part_o, part_ml, seq_lens, bt, maxp, nh, nkv,
                      scale_log2, window, n_splits, counters, prep, no_extra);
   if (rc || n_splits == 1 || counters) return rc;
@@ -581,7 +584,7 @@ static int prefill_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_tiles, nh);
-  const AtExtra no_extra = {0.f, 0.f, nullptr, 0, 0, 1.f};
+  const AtExtra no_extra = {0.f, 0.f, nullptr, 0, 0, 1.f, nullptr, 0};
   return sx_launch(kern, grid, dim3(AT_THREADS), L::SMEM, stream, q, k, v, out, tile_seq, tile_q0, cu, past, lens, bt, maxp, nh,
                    nkv, scale_log2, window, no_extra);
 }
@@ -591,7 +594,8 @@ static int prefill_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out
 // output whose rows are wider than the heads, times a factor.  The single-token form runs one split a (sequence, kv
 // head): with chunks a query sees a few pages at most.
 // ---------------------------------------------------------------------------------------
-static AtExtra make_extra(float scale, float softcap, const float* sinks, int chunk, int out_stride, float out_scale) {
+static AtExtra make_extra(float scale, float softcap, const float* sinks, int chunk, int out_stride, float out_scale,
+                          const float* dist = nullptr, int dist_n = 0) {
   AtExtra ex;
   ex.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   ex.cap_in = softcap > 0.f ? scale / softcap : 0.f;
@@ -599,6 +603,8 @@ static AtExtra make_extra(float scale, float softcap, const float* sinks, int ch
   ex.chunk = chunk;
   ex.out_stride = out_stride;
   ex.out_scale = out_scale;
+  ex.dist = dist_n > 0 ? dist : nullptr;
+  ex.dist_n = dist_n;
   return ex;
 }
 
@@ -618,11 +624,11 @@ extern "C" int sx_attn_prefill_ex(const void* q, const void* k_pages, const void
                                   const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_seqlens,
                                   const int* seq_past, const int* seq_lens, const int* block_table, int maxp, int nh,
                                   int nkv, int hd, float scale, int window, float softcap, const float* sinks, int chunk,
-                                  int out_stride, float out_scale, cudaStream_t stream) {
+                                  int out_stride, float out_scale, const float* dist, int dist_n, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || nh > 65535 || out_stride < nh * hd || (out_stride & 1) || chunk < 0) return SX_ERR_SIZE;
   const float sl = scale * 1.4426950408889634f;
-  const AtExtra ex = make_extra(scale, softcap, sinks, chunk, out_stride, out_scale);
+  const AtExtra ex = make_extra(scale, softcap, sinks, chunk, out_stride, out_scale, dist, dist_n);
   const bf16 *qb = (const bf16*)q, *kb = (const bf16*)k_pages, *vb = (const bf16*)v_pages;
   if (hd == 128) return prefill_ex_launch<128>(qb, kb, vb, (bf16*)out, tile_seq, tile_q0, n_tiles, cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, sl, window, ex, stream);
   if (hd == 64) return prefill_ex_launch<64>(qb, kb, vb, (bf16*)out, tile_seq, tile_q0, n_tiles, cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, sl, window, ex, stream);
@@ -647,12 +653,12 @@ static int decode_ex_launch(const bf16* q, bf16* k, bf16* v, bf16* out, const in
 extern "C" int sx_attn_decode_ex(const void* q, const void* k_pages, const void* v_pages, void* out, const int* seq_lens,
                                  const int* block_table, int maxp, int S, int nh, int nkv, int hd, float scale, int window,
                                  float softcap, const float* sinks, int chunk, int out_stride, float out_scale,
-                                 cudaStream_t stream) {
+                                 const float* dist, int dist_n, cudaStream_t stream) {
   if (S <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || nkv > 65535 || S > 65535 || out_stride < nh * hd || chunk < 0)
     return SX_ERR_SIZE;
   const float sl = scale * 1.4426950408889634f;
-  const AtExtra ex = make_extra(scale, softcap, sinks, chunk, out_stride, out_scale);
+  const AtExtra ex = make_extra(scale, softcap, sinks, chunk, out_stride, out_scale, dist, dist_n);
   const bf16* qb = (const bf16*)q;
   bf16 *kb = (bf16*)const_cast<void*>(k_pages), *vb = (bf16*)const_cast<void*>(v_pages), *ob = (bf16*)out;
   if (hd == 128) return decode_ex_launch<128>(qb, kb, vb, ob, seq_lens, block_table, maxp, S, nh, nkv, sl, window, ex, stream);

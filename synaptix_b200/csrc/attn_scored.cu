@@ -19,7 +19,7 @@
 __device__ __forceinline__ float sigmoid_acc(float x) { return 1.f / (1.f + expf(-x)); }
 
 // ---------------------------------------------------------------------------------------
-// head preparation: one block a token, a warp a head at a time
+// head preparation: grid (tokens, groups of four heads), a warp a head
 // ---------------------------------------------------------------------------------------
 struct PrepArgs {
   const float* proj; int row; const float* bias;
@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(128) heads_prepare_kernel(const PrepArgs a) {
   const int half = a.inv_freq ? a.rot_dims / 2 : 0;
   const float lam = (a.v_first_in && a.lam) ? *a.lam : 0.f;
 
-  for (int head = warp; head < H + 2 * G; head += 4) {
+  for (int head = blockIdx.y * 4 + warp; head < H + 2 * G; head += 4 * gridDim.y) {
     const bool is_q = head < H, is_k = !is_q && head < H + G;
     if (is_q || is_k) {
       const int col = head * dim;
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(128) heads_prepare_kernel(const PrepArgs a) {
       }
     }
   }
-  if (a.gate_out) {
+  if (a.gate_out && blockIdx.y == 0) {
     const int col = (H + G) * dim + G * vdim;
     for (int i = threadIdx.x; i < a.n_gate; i += blockDim.x)
       a.gate_out[(size_t)t * a.n_gate + i] = sigmoid_acc(src_tok[col + i] + (a.bias ? a.bias[col + i] : 0.f));
@@ -116,8 +116,11 @@ extern "C" int sx_heads_prepare(const float* proj, int row, const float* bias, v
   a.H = H; a.G = G; a.dim = dim; a.vdim = vdim; a.qn = qn; a.kn = kn; a.eps = eps; a.inv_freq = inv_freq;
   a.rot_dims = rot_dims; a.mag = mag; a.v_first_in = v_first_in; a.v_first_out = v_first_out; a.lam = lam;
   a.gate_out = gate_out; a.n_gate = n_gate;
-  if (dt == SX_F32) return sx_launch(heads_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, a);
-  if (dt == SX_BF16) return sx_launch(heads_prepare_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, a);
+  // few tokens: a block for every four heads, so that a single token's heads spread over the GPU
+  const int groups = (H + 2 * G + 3) / 4;
+  const dim3 grid(n_tokens, n_tokens >= 1024 ? 1 : (groups > 65535 ? 65535 : groups));
+  if (dt == SX_F32) return sx_launch(heads_prepare_kernel<float>, grid, dim3(128), 0, stream, a);
+  if (dt == SX_BF16) return sx_launch(heads_prepare_kernel<bf16>, grid, dim3(128), 0, stream, a);
   return SX_ERR_DTYPE;
 }
 
@@ -370,20 +373,22 @@ __global__ void __launch_bounds__(SC_THREADS) attn_scored_kernel(const ScArgs a)
   }
 }
 
-// the chunks of a token's keys added up in chunk order
+// the chunks of a token's keys added up in chunk order: a block a (token, head), a thread a value element
 template <typename T>
 __global__ void __launch_bounds__(128) attn_scored_merge_kernel(const float* __restrict__ part, const float* __restrict__ part_ml,
                                                                 T* __restrict__ out, const float* __restrict__ gate, int H, int vdim,
                                                                 int n_chunks, int softmax, int out_stride) {
   pdl_wait();
   pdl_trigger();
-  const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < H * vdim; i += blockDim.x) {
-    const int h = i / vdim;
-    float m = -INFINITY;
-    if (softmax)
-      for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, part_ml[(((size_t)t * n_chunks + c) * H + h) * 2]);
+  const int t = blockIdx.x, h = blockIdx.y;
+  float m = -INFINITY;
+  if (softmax)
+    for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, part_ml[(((size_t)t * n_chunks + c) * H + h) * 2]);
+  const float g = gate ? gate[(size_t)t * H + h] : 1.f;
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    const int i = h * vdim + d;
     float o = 0.f, l = 0.f;
+#pragma unroll 4
     for (int c = 0; c < n_chunks; ++c) {
       float f = 1.f;
       if (softmax) {
@@ -394,8 +399,7 @@ __global__ void __launch_bounds__(128) attn_scored_merge_kernel(const float* __r
       o = fmaf(f, part[((size_t)t * n_chunks + c) * H * vdim + i], o);
     }
     if (softmax) o = l > 0.f ? o / l : 0.f;
-    if (gate) o *= gate[(size_t)t * H + h];
-    out[(size_t)t * out_stride + i] = from_f32<T>(o);
+    out[(size_t)t * out_stride + i] = from_f32<T>(o * g);
   }
 }
 
@@ -449,9 +453,10 @@ extern "C" int sx_attn_scored(const void* q, const void* k_pages, const void* v_
   else if (dt == SX_BF16) rc = tq == 4 ? scored_pick<bf16, 4>(a, n_tiles, stream) : scored_pick<bf16, 1>(a, n_tiles, stream);
   else return SX_ERR_DTYPE;
   if (rc != 0 || n_chunks == 1) return rc;
+  const int mt = vdim <= 32 ? 32 : (vdim <= 64 ? 64 : 128);
   if (dt == SX_F32)
-    return sx_launch(attn_scored_merge_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)part,
+    return sx_launch(attn_scored_merge_kernel<float>, dim3(n_tokens, H), dim3(mt), 0, stream, (const float*)part,
                      (const float*)part_ml, (float*)out, gate, H, vdim, n_chunks, softmax, out_stride);
-  return sx_launch(attn_scored_merge_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, (const float*)part,
+  return sx_launch(attn_scored_merge_kernel<bf16>, dim3(n_tokens, H), dim3(mt), 0, stream, (const float*)part,
                    (const float*)part_ml, (bf16*)out, gate, H, vdim, n_chunks, softmax, out_stride);
 }

@@ -66,7 +66,10 @@ __device__ __forceinline__ void load_page(unsigned char* stage, const bf16* __re
 //   jbase  absolute index of the page's first key
 // With EX (further options, see AtExtra): keys below low_lo / low_hi are masked for the two rows (the first key of the
 // row's chunk of positions), and with a cap the raw scores become cap * tanh(score * scale / cap) * log2(e) at once,
-// so that everything behind (the running maximum, the exponent) works on them with a scale of 1.
+// so that everything behind (the running maximum, the exponent) works on them with a scale of 1.  With a distance
+// table (dist_lo / dist_hi: the rows of the table for the heads of fragment rows g and g + 8, dist_n entries each) the
+// score of the query at position p against key j becomes score * scale + table[min(p - j, dist_n - 1)], again in the
+// log2 domain with a scale of 1 behind.
 // ---------------------------------------------------------------------------------------
 struct AtExtra {
   float cap_log2;        // softcap * log2(e), 0: no cap
@@ -75,6 +78,8 @@ struct AtExtra {
   int chunk;             // > 0: a query sees only keys of its own chunk of that many positions
   int out_stride;        // elements between two tokens' rows of the output
   float out_scale;       // the output is multiplied by this
+  const float* dist;     // [nh, dist_n] or null: a number per head and distance, added to the scaled score
+  int dist_n;            // distances from dist_n - 1 on share the last entry
 };
 
 template <int HD, int NKT, bool MASKED, bool EX = false>
@@ -82,7 +87,8 @@ __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], co
                                             const unsigned char* vst, int key0, int jbase, int pos_lo, int pos_hi,
                                             int window, float scale_log2, float (&m)[2], float (&l)[2],
                                             float (&o)[HD / 8][4], int low_lo = 0, int low_hi = 0, float cap_log2 = 0.f,
-                                            float cap_in = 0.f) {
+                                            float cap_in = 0.f, const float* dist_lo = nullptr,
+                                            const float* dist_hi = nullptr, int dist_n = 0) {
   using L = AtLayout<HD>;
   const int lane = threadIdx.x & 31, t = lane & 3;
   float s[NKT][4];
@@ -121,6 +127,18 @@ __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], co
         // cap turns into a few 1e-5 of a score (tanhf would cost five times the instructions for every score)
         const float ex = __expf(2.f * s[kt][e] * cap_in);
         s[kt][e] = cap_log2 * (1.f - __fdividef(2.f, ex + 1.f));
+      }
+    scale_log2 = 1.f;
+  }
+  if (EX && dist_lo != nullptr) {
+#pragma unroll
+    for (int kt = 0; kt < NKT; ++kt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = jbase + key0 + kt * 8 + 2 * t + (e & 1);
+        const int p = (e < 2) ? pos_lo : pos_hi;
+        const int d = min(max(p - j, 0), dist_n - 1);             // keys behind the query are masked below
+        s[kt][e] = fmaf(s[kt][e], scale_log2, 1.4426950408889634f * __ldg(((e < 2) ? dist_lo : dist_hi) + d));
       }
     scale_log2 = 1.f;
   }

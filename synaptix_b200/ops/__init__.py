@@ -25,7 +25,7 @@ from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, e
 from .sequence import add_rmsnorm_conv, capped_glu, mingru, retention, stream_add
 from .block import add_scaled, add_scaled_rmsnorm, scale_rows
 from .layernorm import add_layernorm
-from .scored import attn_scored, heads_prepare
+from .scored import attn_scored as attn_scored_all_heads, heads_prepare
 from .latent import (head_gate, latent_attention, latent_expand, latent_gather, latent_output, latent_prepare, latent_query,
                      latent_rotate_q)
 from .mlstm import mlstm
@@ -286,6 +286,23 @@ def _query_tiles(ctx, rows: int, device):
         both = torch.from_numpy(np.asarray([ts, t0], dtype=np.int32)).to(device, non_blocking=True)
         tiles = ctx.scratch[("query_tiles", rows)] = (both[0], both[1])
     return tiles
+
+
+def attn_scored(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx, block_table: torch.Tensor, H: int,
+                G: int, dim: int, vdim: int, scale: float, window: Optional[int], *, talk=None, head_bias=None,
+                dist_bias=None, softmax: bool = False, gate=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention whose weights may depend on all heads' scores (see ``scored.attn_scored``).  Where every head stands
+    alone (softmax, no mixture over heads, no gate), keys and values share one of the mma.sync kernels' head sizes and
+    the step brings portions of prompts, that kernel takes the step with the distance table as one of its options; a
+    number per head cancels in a softmax and is left out there."""
+    if (softmax and talk is None and gate is None and out is None and vdim == dim and not ctx.all_single
+            and ctx.host is not None and fast_supported(q.dtype, H, G, dim) and k_pages.dtype == q.dtype
+            and OPTIONS.attn_options_fast and ctx.max_new >= 16):
+        tiles = _query_tiles(ctx, 64, q.device)
+        return attn_prefill_ex(q, k_pages, v_pages, tiles[0], tiles[1], ctx.cu_seqlens, ctx.seq_past, ctx.seq_lens,
+                               block_table, H, G, dim, scale, window, dist=dist_bias)
+    return attn_scored_all_heads(q, k_pages, v_pages, ctx, block_table, H, G, dim, vdim, scale, window, talk=talk,
+                                 head_bias=head_bias, dist_bias=dist_bias, softmax=softmax, gate=gate, out=out)
 
 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx, block_table: torch.Tensor,

@@ -209,8 +209,9 @@ def attn_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
     return out
 
 
-def _ex_args(q, nh, hd, softcap, sinks, chunk, out, out_col, out_scale, rows):
-    """The further options of the two mma.sync kernels (capped scores, sinks, chunks, a wider output) as ctypes."""
+def _ex_args(q, nh, hd, softcap, sinks, chunk, out, out_col, out_scale, rows, dist=None):
+    """The further options of the two mma.sync kernels (capped scores, sinks, chunks, a wider output, a number per head
+    and distance) as ctypes."""
     if out is None:
         out = torch.empty((rows, nh * hd), dtype=q.dtype, device=q.device)
     if out.dtype != q.dtype or out.shape[0] != rows or out_col + nh * hd > out.shape[1] or not out.is_contiguous():
@@ -219,22 +220,27 @@ def _ex_args(q, nh, hd, softcap, sinks, chunk, out, out_col, out_scale, rows):
         raise KernelError("attention: the output's columns must begin and end at even places")
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nh):
         raise KernelError("attention: sinks are float32, one per query head")
+    if dist is not None and (dist.dtype != torch.float32 or dist.dim() != 2 or dist.shape[0] != nh or not dist.is_contiguous()):
+        raise KernelError("attention: the distance table is float32 [heads, distances]")
     o = out if out_col == 0 else out.view(-1)[out_col:]
     return out, (c_float(0.0 if softcap is None else float(softcap)), ptr(sinks), c_int(0 if chunk is None else int(chunk)),
-                 c_int(out.shape[1]), c_float(out_scale)), o
+                 c_int(out.shape[1]), c_float(out_scale), ptr(dist), c_int(0 if dist is None else dist.shape[1])), o
 
 
 def attn_prefill_ex(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, tile_seq: torch.Tensor,
                     tile_q0: torch.Tensor, cu_seqlens: torch.Tensor, seq_past: torch.Tensor, seq_lens: torch.Tensor,
                     block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: Optional[int], *,
                     softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                    out: Optional[torch.Tensor] = None, out_col: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+                    out: Optional[torch.Tensor] = None, out_col: int = 0, out_scale: float = 1.0,
+                    dist: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``attn_prefill`` with capped scores (``softcap * tanh(score / softcap)``), a sink per head in the softmax's
-    denominator, chunks of positions, and the result times ``out_scale`` in the columns of ``out`` from ``out_col`` on."""
-    require_cuda(q, k_pages, v_pages, tile_seq, tile_q0, cu_seqlens, seq_past, seq_lens, block_table, out, sinks)
+    denominator, chunks of positions, a learned number per head and distance added to the scaled score (``dist`` float32
+    ``[heads, n]``, distance ``d`` reads column ``min(d, n - 1)``), and the result times ``out_scale`` in the columns of
+    ``out`` from ``out_col`` on."""
+    require_cuda(q, k_pages, v_pages, tile_seq, tile_q0, cu_seqlens, seq_past, seq_lens, block_table, out, sinks, dist)
     if not fast_supported(q.dtype, nh, nkv, hd) or k_pages.dtype != q.dtype:
         raise KernelError("attn_prefill_ex: bfloat16 and head size 32/64/128")
-    out, extra, o = _ex_args(q, nh, hd, softcap, sinks, chunk, out, out_col, out_scale, q.shape[0])
+    out, extra, o = _ex_args(q, nh, hd, softcap, sinks, chunk, out, out_col, out_scale, q.shape[0], dist)
     check(fn("attention", "sx_attn_prefill_ex")(
         ptr(q), ptr(k_pages), ptr(v_pages), ptr(o), ptr(tile_seq), ptr(tile_q0), c_int(tile_seq.numel()),
         ptr(cu_seqlens), ptr(seq_past), ptr(seq_lens), ptr(block_table), c_int(block_table.shape[1]), c_int(nh),
@@ -245,13 +251,14 @@ def attn_prefill_ex(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
 def attn_decode_ex(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, seq_lens: torch.Tensor,
                    block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: Optional[int], *,
                    softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                   out: Optional[torch.Tensor] = None, out_col: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+                   out: Optional[torch.Tensor] = None, out_col: int = 0, out_scale: float = 1.0,
+                   dist: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``attn_decode`` (one query token per sequence) with the same options as ``attn_prefill_ex``; one block per
     (sequence, kv head) takes all the pages the query sees."""
-    require_cuda(q, k_pages, v_pages, seq_lens, block_table, out, sinks)
+    require_cuda(q, k_pages, v_pages, seq_lens, block_table, out, sinks, dist)
     if not fast_supported(q.dtype, nh, nkv, hd) or k_pages.dtype != q.dtype:
         raise KernelError("attn_decode_ex: bfloat16, head size 32/64/128 and at most 16 query heads per kv head")
-    out, extra, o = _ex_args(q, nh, hd, softcap, sinks, chunk, out, out_col, out_scale, q.shape[0])
+    out, extra, o = _ex_args(q, nh, hd, softcap, sinks, chunk, out, out_col, out_scale, q.shape[0], dist)
     check(fn("attention", "sx_attn_decode_ex")(
         ptr(q), ptr(k_pages), ptr(v_pages), ptr(o), ptr(seq_lens), ptr(block_table), c_int(block_table.shape[1]),
         c_int(q.shape[0]), c_int(nh), c_int(nkv), c_int(hd), c_float(scale), c_int(0 if window is None else int(window)),

@@ -63,7 +63,7 @@ def _chunks(n_tokens: int, max_len: int, window: Optional[int], device) -> int:
     tiles = max(1, (keys + 31) // 32 + 1)
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     want = max(1, (2 * sms) // max(1, n_tokens))
-    return max(1, min(want, (tiles + 3) // 4, 32))
+    return max(1, min(want, tiles, 64))
 
 
 def attn_scored(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx, block_table: torch.Tensor, H: int,

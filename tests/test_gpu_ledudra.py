@@ -197,7 +197,8 @@ def test_sigmoid_attention_with_scores_mixed_over_heads(H, G, D, Dv, window, dty
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,Dv,window,rows,far", [(4, 2, 8, 12, 70, 10, 50), (8, 2, 64, 32, 136, 16, 120), (3, 3, 16, 16, None, 2, 3),
-                                                       (2, 1, 24, 20, 9, 6, 7), (4, 1, 64, 64, 130, 32, 128)])
+                                                       (2, 1, 24, 20, 9, 6, 7), (4, 1, 64, 64, 130, 32, 128), (6, 2, 32, 32, None, 12, 40),
+                                                       (4, 2, 128, 128, 70, 8, 200), (16, 1, 64, 64, 64, 64, 65)])
 def test_softmax_attention_with_a_bias_per_distance_bucket(H, G, D, Dv, window, rows, far, dtype):
     """The table holds large numbers, one bucket after the other favoured per head, so a distance that falls into the
     wrong bucket moves the weights by far more than the tolerance; the last bucket (every far distance) among them."""
@@ -217,7 +218,9 @@ def test_softmax_attention_with_a_bias_per_distance_bucket(H, G, D, Dv, window, 
     cols = distance_columns(rows, far, window)
     table = rel[torch.from_numpy(cols)].t().contiguous().cuda()
     tol = dict(atol=1e-4, rtol=1e-4) if dtype == "float32" else dict(atol=4e-2, rtol=3e-2)
-    for steps in ([(0, cut)] + [(p, 1) for p in range(cut, T)], [(p, 5) for p in range(0, T, 5)]):
+    # the last schedule's portions start and end inside pages and inside the 64-row tiles of the tensor-core kernel
+    for steps in ([(0, cut)] + [(p, 1) for p in range(cut, T)], [(p, 5) for p in range(0, T, 5)],
+                  [(0, 100), (100, 64), (164, 17), (181, T - 181)]):
         got = _run_attention(q, k, v, H, G, D, Dv, scale, window, steps, dt, dist_bias=table, softmax=True)
         assert torch.allclose(got.double(), ref, **tol), float((got.double() - ref).abs().max())
 
