@@ -236,7 +236,8 @@ __global__ void __launch_bounds__(SC_THREADS) attn_scored_kernel(const ScArgs a)
       if (j0 + j <= last_pos) {
         const T* kr = kp + (((size_t)page * G + c) * SX_PAGE + prow + j) * dim;
         if (kvec) {
-          for (int d = 0; d < dim; d += KV) {
+#pragma unroll 4
+          for (int d = 0; d < dim; d += KV) {            // (unrolled: several 16-byte loads of the key in flight)
             float kf[KV];
             sc_io<T>::ld16(kr + d, kf);
 #pragma unroll
@@ -309,6 +310,7 @@ __global__ void __launch_bounds__(SC_THREADS) attn_scored_kernel(const ScArgs a)
       }
       const int nj = min(SC_KT, last_pos - j0 + 1);
       const T* vr0 = vp + (((size_t)page * G + c3) * SX_PAGE + prow) * vdim + d0;
+#pragma unroll 2
       for (int j = 0; j < nj; j += 4) {
         float vf[4][4];
 #pragma unroll
@@ -388,7 +390,7 @@ __global__ void __launch_bounds__(128) attn_scored_merge_kernel(const float* __r
   for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
     const int i = h * vdim + d;
     float o = 0.f, l = 0.f;
-#pragma unroll 4
+#pragma unroll 16
     for (int c = 0; c < n_chunks; ++c) {
       float f = 1.f;
       if (softmax) {
@@ -459,4 +461,239 @@ extern "C" int sx_attn_scored(const void* q, const void* k_pages, const void* v_
                      (const float*)part_ml, (float*)out, gate, H, vdim, n_chunks, softmax, out_stride);
   return sx_launch(attn_scored_merge_kernel<bf16>, dim3(n_tokens, H), dim3(mt), 0, stream, (const float*)part,
                    (const float*)part_ml, (bf16*)out, gate, H, vdim, n_chunks, softmax, out_stride);
+}
+
+// =======================================================================================
+// Prompt portions with sigmoid weights on the tensor cores (bfloat16 cache, mma.sync m16n8k16).
+//
+// A block takes up to 8 consecutive rows of one sequence and ALL heads, and walks the visible keys 16 at a time:
+//   1  raw scores, keys as the rows of the product:  S^T_g [16 keys x 8 queries] = K_kv(g) [16 x dim] Q_g^T, into
+//      shared memory as float32 times scale (warp w: heads w * HPW ..);
+//   2  the mixture over heads in FFMA, a thread a (key, query) pair and half of the heads; bias, mask, sigmoid; the
+//      weights go to shared memory as bfloat16 [head][query][key];
+//   3  O^T_h [vdim x 8 queries] += V_kv(h)^T [vdim x 16 keys] P_h^T  (warp w: the same heads; the sums stay in registers,
+//      HPW * vdim / 4 of them a thread, which is what limits a block to 8 rows).
+// The next keys are fetched while the scores are mixed, the values while the raw scores are formed.
+// H = 8 * HPW heads exactly; DIM and VD are 64 or 128.
+// =======================================================================================
+#include "attn_tile.cuh"
+
+#define TK_THREADS 256
+#define TK_KT 16
+#define TK_TQ 8
+
+template <int HPW, int DIM, int VD> struct TkLayout {
+  static constexpr int H = 8 * HPW;
+  static constexpr int QROW = DIM * 2 + 16, VROW = VD * 2 + 16, PROW = TK_KT * 2 + 16;
+  static constexpr int Q_BYTES = H * TK_TQ * QROW;
+  static constexpr int S_BYTES = H * TK_KT * TK_TQ * 4;
+  static constexpr int P_BYTES = H * TK_TQ * PROW;
+  static constexpr int T_BYTES = H * H * 4;
+  static size_t bytes(int G) { return (size_t)Q_BYTES + S_BYTES + P_BYTES + T_BYTES + (size_t)G * TK_KT * (QROW + VROW); }
+};
+
+struct TkArgs {
+  const bf16* q; const bf16* k_pages; const bf16* v_pages; bf16* out;
+  const int* positions; const int* seq_of_token; const int* block_table; int maxp;
+  const int* tile_tok0; const int* tile_rows;
+  int G; float scale; int window;
+  const float* talk; const float* head_bias; const float* gate; int out_stride;
+};
+
+// rows j0 .. j0+15 of every kv head's page -> dst [G][16][ROWB]; rows outside [lo, hi] are zero-filled
+template <int ELEMS, int ROWB>
+__device__ __forceinline__ void tk_load(unsigned char* dst, const bf16* pages, int page, int G, int j0, int lo, int hi) {
+  constexpr int CH = ELEMS / 8;
+  const int prow = j0 & 63;
+  for (int i = threadIdx.x; i < G * TK_KT * CH; i += TK_THREADS) {
+    const int ch = i % CH, r = (i / CH) % TK_KT, c = i / (CH * TK_KT);
+    const bool ok = j0 + r >= lo && j0 + r <= hi;
+    const bf16* src = pages + (((size_t)page * G + c) * SX_PAGE + prow + (ok ? r : 0)) * ELEMS + ch * 8;
+    cp_async16(smem_addr(dst + ((size_t)c * TK_KT + r) * ROWB + ch * 16), src, ok);
+  }
+}
+
+template <int HPW, int DIM, int VD>
+__global__ void __launch_bounds__(TK_THREADS, 1) attn_talk_prefill_kernel(const TkArgs a) {
+  using L = TkLayout<HPW, DIM, VD>;
+  constexpr int H = L::H;
+  extern __shared__ __align__(16) unsigned char tk_smem[];
+  __shared__ int pos_q[TK_TQ];
+  pdl_wait();
+  pdl_trigger();
+  unsigned char* Qs = tk_smem;
+  float* S = reinterpret_cast<float*>(Qs + L::Q_BYTES);
+  unsigned char* Ps = reinterpret_cast<unsigned char*>(S) + L::S_BYTES;
+  float* talk = reinterpret_cast<float*>(Ps + L::P_BYTES);
+  unsigned char* Ks = reinterpret_cast<unsigned char*>(talk) + L::T_BYTES;
+  const int G = a.G, per = H / G;
+  unsigned char* Vs = Ks + (size_t)G * TK_KT * L::QROW;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int tile = gridDim.x - 1 - blockIdx.x;               // late rows see the most keys: first
+  const int tok0 = a.tile_tok0[tile], rows = min(TK_TQ, a.tile_rows[tile]);
+  if (tid < TK_TQ) pos_q[tid] = tid < rows ? a.positions[tok0 + tid] : -1;
+  const int first_pos = a.positions[tok0], last_pos = first_pos + rows - 1;
+  const int lo = a.window > 0 ? max(0, first_pos - a.window + 1) : 0;
+  const int* bt = a.block_table + (size_t)a.seq_of_token[tok0] * a.maxp;
+  const int j_begin = lo & ~(TK_KT - 1);
+
+  // queries: [head][row][dim], rows beyond the tile zero
+  for (int i = tid; i < H * TK_TQ * (DIM / 8); i += TK_THREADS) {
+    const int ch = i % (DIM / 8), r = (i / (DIM / 8)) % TK_TQ, h = i / (DIM / 8 * TK_TQ);
+    const bool ok = r < rows;
+    cp_async16(smem_addr(Qs + ((size_t)h * TK_TQ + r) * L::QROW + ch * 16),
+               a.q + ((size_t)(tok0 + (ok ? r : 0)) * H + h) * DIM + ch * 8, ok);
+  }
+  tk_load<DIM, L::QROW>(Ks, a.k_pages, bt[j_begin >> 6], G, j_begin, lo, last_pos);
+  cp_async_commit();
+  for (int i = tid; i < H * H; i += TK_THREADS) talk[i] = a.talk ? a.talk[i] : ((i / H == i % H) ? 1.f : 0.f);
+
+  float o[HPW][VD / 16][4];
+#pragma unroll
+  for (int r = 0; r < HPW; ++r)
+#pragma unroll
+    for (int n = 0; n < VD / 16; ++n) o[r][n][0] = o[r][n][1] = o[r][n][2] = o[r][n][3] = 0.f;
+
+  for (int j0 = j_begin; j0 <= last_pos; j0 += TK_KT) {
+    tk_load<VD, L::VROW>(Vs, a.v_pages, bt[j0 >> 6], G, j0, lo, last_pos);
+    cp_async_commit();
+    cp_async_wait<1>();                                       // the keys (and, the first time, the queries)
+    __syncthreads();
+    // 1: raw scores
+#pragma unroll
+    for (int r = 0; r < HPW; ++r) {
+      const int h = warp * HPW + r, c = h / per;
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t ka = smem_addr(Ks + ((size_t)c * TK_KT + (lane & 7) + ((lane >> 3) & 1) * 8) * L::QROW + (lane >> 4) * 16);
+      const uint32_t qa = smem_addr(Qs + ((size_t)h * TK_TQ + (lane & 7)) * L::QROW + (lane >> 3) * 16);
+#pragma unroll
+      for (int d = 0; d < DIM / 32; ++d) {
+        uint32_t b0, b1, b2, b3, a0[4], a1[4];
+        ldsm_x4(b0, b1, b2, b3, qa + d * 64);
+        ldsm_x4(a0[0], a0[1], a0[2], a0[3], ka + d * 64);
+        ldsm_x4(a1[0], a1[1], a1[2], a1[3], ka + d * 64 + 32);
+        mma16816(s, a0, b0, b1);
+        mma16816(s, a1, b2, b3);
+      }
+      float* sh = S + h * (TK_KT * TK_TQ);
+      *reinterpret_cast<float2*>(sh + g * TK_TQ + 2 * t) = make_float2(s[0] * a.scale, s[1] * a.scale);
+      *reinterpret_cast<float2*>(sh + (g + 8) * TK_TQ + 2 * t) = make_float2(s[2] * a.scale, s[3] * a.scale);
+    }
+    __syncthreads();
+    if (j0 + TK_KT <= last_pos) tk_load<DIM, L::QROW>(Ks, a.k_pages, bt[(j0 + TK_KT) >> 6], G, j0 + TK_KT, lo, last_pos);
+    cp_async_commit();
+    // 2: mixture over heads, bias, mask, sigmoid
+    {
+      const int pair = tid & (TK_KT * TK_TQ - 1), half = tid >> 7;
+      const int key = pair >> 3, qi = pair & 7;
+      const int pq = pos_q[qi], jk = j0 + key;
+      const bool vis = pq >= 0 && jk <= pq && (a.window == 0 || jk > pq - a.window);
+      float raw[H];
+#pragma unroll
+      for (int gg = 0; gg < H; ++gg) raw[gg] = S[gg * (TK_KT * TK_TQ) + pair];
+#pragma unroll
+      for (int hh = 0; hh < H / 2; ++hh) {
+        const int h = half * (H / 2) + hh;
+        const float4* tr = reinterpret_cast<const float4*>(talk + h * H);
+        float acc = 0.f;
+#pragma unroll
+        for (int g4 = 0; g4 < H / 4; ++g4) {
+          const float4 w4 = tr[g4];
+          acc = fmaf(w4.x, raw[4 * g4], acc); acc = fmaf(w4.y, raw[4 * g4 + 1], acc);
+          acc = fmaf(w4.z, raw[4 * g4 + 2], acc); acc = fmaf(w4.w, raw[4 * g4 + 3], acc);
+        }
+        if (a.head_bias) acc += a.head_bias[h];
+        const float w = vis ? sigmoid_acc(acc) : 0.f;
+        *reinterpret_cast<bf16*>(Ps + ((size_t)h * TK_TQ + qi) * L::PROW + key * 2) = __float2bfloat16_rn(w);
+      }
+    }
+    cp_async_wait<1>();                                       // the values
+    __syncthreads();
+    // 3: weighted sums of the values
+    {
+      int c_have = -1;
+      uint32_t va[VD / 16][4];
+      const int lm = lane >> 3;
+#pragma unroll
+      for (int r = 0; r < HPW; ++r) {
+        const int h = warp * HPW + r, c = h / per;
+        if (c != c_have) {
+          c_have = c;
+          const uint32_t vaddr = smem_addr(Vs + ((size_t)c * TK_KT + (lane & 7) + (lm >> 1) * 8) * L::VROW + (lm & 1) * 16);
+#pragma unroll
+          for (int n = 0; n < VD / 16; ++n) ldsm_x4_trans(va[n][0], va[n][1], va[n][2], va[n][3], vaddr + n * 32);
+        }
+        const unsigned char* pr = Ps + ((size_t)h * TK_TQ + g) * L::PROW + 4 * t;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(pr), b1 = *reinterpret_cast<const uint32_t*>(pr + 16);
+#pragma unroll
+        for (int n = 0; n < VD / 16; ++n) mma16816(o[r][n], va[n], b0, b1);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // o[r][n]: value elements n*16 + g (+8) of queries 2t, 2t+1
+#pragma unroll
+  for (int r = 0; r < HPW; ++r) {
+    const int h = warp * HPW + r;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int qi = 2 * t + e;
+      if (qi >= rows) continue;
+      const float f = a.gate ? a.gate[(size_t)(tok0 + qi) * H + h] : 1.f;
+      bf16* orow = a.out + (size_t)(tok0 + qi) * a.out_stride + (size_t)h * VD;
+#pragma unroll
+      for (int n = 0; n < VD / 16; ++n) {
+        orow[n * 16 + g] = __float2bfloat16_rn(o[r][n][e] * f);
+        orow[n * 16 + g + 8] = __float2bfloat16_rn(o[r][n][2 + e] * f);
+      }
+    }
+  }
+}
+
+template <int HPW, int DIM, int VD>
+static int talk_launch(const TkArgs& a, int n_tiles, cudaStream_t stream) {
+  const size_t smem = TkLayout<HPW, DIM, VD>::bytes(a.G);
+  if (smem > 220 * 1024) return SX_ERR_SIZE;
+  cudaError_t e = cudaFuncSetAttribute(attn_talk_prefill_kernel<HPW, DIM, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  return sx_launch(attn_talk_prefill_kernel<HPW, DIM, VD>, dim3(n_tiles), dim3(TK_THREADS), smem, stream, a);
+}
+
+template <int HPW>
+static int talk_pick(const TkArgs& a, int n_tiles, int dim, int vdim, cudaStream_t stream) {
+  if (dim == 128 && vdim == 128) return talk_launch<HPW, 128, 128>(a, n_tiles, stream);
+  if (dim == 64 && vdim == 64) return talk_launch<HPW, 64, 64>(a, n_tiles, stream);
+  if (dim == 128 && vdim == 64) return talk_launch<HPW, 128, 64>(a, n_tiles, stream);
+  if (dim == 64 && vdim == 128) return talk_launch<HPW, 64, 128>(a, n_tiles, stream);
+  return SX_ERR_SIZE;
+}
+
+// bytes of shared memory a block of the tensor-core prompt kernel needs, or -1 where it does not apply
+extern "C" int sx_attn_talk_prefill_smem(int H, int G, int dim, int vdim) {
+  if ((H != 8 && H != 16 && H != 32) || G <= 0 || H % G || (dim != 64 && dim != 128) || (vdim != 64 && vdim != 128)) return -1;
+  const size_t row = (size_t)dim * 2 + 16, vrow = (size_t)vdim * 2 + 16;
+  return (int)((size_t)H * TK_TQ * row + (size_t)H * TK_KT * TK_TQ * 4 + (size_t)H * TK_TQ * (TK_KT * 2 + 16) +
+                     (size_t)H * H * 4 + (size_t)G * TK_KT * (row + vrow));
+}
+
+// tiles: up to 8 consecutive rows of one sequence each.  Sigmoid weights only; talk, head_bias and gate may be null.
+extern "C" int sx_attn_talk_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* positions,
+                                    const int* seq_of_token, const int* block_table, int maxp, const int* tile_tok0,
+                                    const int* tile_rows, int n_tiles, int H, int G, int dim, int vdim, float scale, int window,
+                                    const float* talk, const float* head_bias, const float* gate, int out_stride,
+                                    cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (sx_attn_talk_prefill_smem(H, G, dim, vdim) < 0 || out_stride < H * vdim || !tile_tok0 || !tile_rows) return SX_ERR_SIZE;
+  if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return SX_ERR_ALIGN;
+  TkArgs a;
+  a.q = (const bf16*)q; a.k_pages = (const bf16*)k_pages; a.v_pages = (const bf16*)v_pages; a.out = (bf16*)out;
+  a.positions = positions; a.seq_of_token = seq_of_token; a.block_table = block_table; a.maxp = maxp;
+  a.tile_tok0 = tile_tok0; a.tile_rows = tile_rows; a.G = G; a.scale = scale; a.window = window; a.talk = talk;
+  a.head_bias = head_bias; a.gate = gate; a.out_stride = out_stride;
+  if (H == 32) return talk_pick<4>(a, n_tiles, dim, vdim, stream);
+  if (H == 16) return talk_pick<2>(a, n_tiles, dim, vdim, stream);
+  return talk_pick<1>(a, n_tiles, dim, vdim, stream);
 }

@@ -30,63 +30,145 @@ struct LnArgs {
   int W;
 };
 
-__device__ __forceinline__ float ln_load_delta(const LnArgs& a, size_t i) {
-  return a.delta_dt == SX_F32 ? ((const float*)a.delta)[i] : __bfloat162float(((const bf16*)a.delta)[i]);
+// V elements at a time (4 where the width is a multiple of 4: 16-byte loads, so that a row is a few loads a thread and the
+// loads of one pass are all in flight together)
+template <int V> __device__ __forceinline__ void ln_ld(const float* p, float* f) {
+  if (V == 4) { const float4 u = *reinterpret_cast<const float4*>(p); f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w; }
+  else f[0] = *p;
+}
+template <int V> __device__ __forceinline__ void ln_st(float* p, const float* f) {
+  if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  else *p = f[0];
+}
+template <int V> __device__ __forceinline__ void ln_st_out(float* p, const float* f) { ln_st<V>(p, f); }
+template <int V> __device__ __forceinline__ void ln_st_out(bf16* p, const float* f) {
+  if (V == 4) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(f[0], f[1]), hi = __floats2bfloat162_rn(f[2], f[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else {
+    *p = __float2bfloat16_rn(f[0]);
+  }
+}
+template <int V> __device__ __forceinline__ void ln_ld_delta(const LnArgs& a, size_t i, float* f) {
+  if (a.delta_dt == SX_F32) { ln_ld<V>((const float*)a.delta + i, f); return; }
+  const bf16* p = (const bf16*)a.delta + i;
+  if (V == 4) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    f[0] = x.x; f[1] = x.y; f[2] = y.x; f[3] = y.y;
+  } else {
+    f[0] = __bfloat162float(*p);
+  }
 }
 
 // the row t after the sum, left in `row` (shared, W floats); returns mean and 1/sqrt(var + eps) of it
+template <int V>
 __device__ void ln_row(const LnArgs& a, int t, float* row, float* red, float& mean, float& rstd) {
-  const int W = a.W;
+  const int W = a.W, c0 = threadIdx.x * V, step = blockDim.x * V;
   const float invW = 1.f / (float)W;
   const size_t base = (size_t)t * W;
+  float s = 0.f;
   if (a.delta) {
-    float s = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-      const float d = ln_load_delta(a, base + c) + (a.dbias ? a.dbias[c] : 0.f);
-      row[c] = d;
-      s += d;
+    for (int c = c0; c < W; c += step) {
+      float d[V], e[V];
+      ln_ld_delta<V>(a, base + c, d);
+      if (a.dbias) {
+        ln_ld<V>(a.dbias + c, e);
+#pragma unroll
+        for (int i = 0; i < V; ++i) d[i] += e[i];
+      }
+      ln_st<V>(row + c, d);
+#pragma unroll
+      for (int i = 0; i < V; ++i) s += d[i];
     }
     if (a.pw) {
       const float mu = block_sum(s, red) * invW;
       float v = 0.f;
-      for (int c = threadIdx.x; c < W; c += blockDim.x) { const float d = row[c] - mu; v += d * d; }
+      for (int c = c0; c < W; c += step) {
+        float d[V];
+        ln_ld<V>(row + c, d);
+#pragma unroll
+        for (int i = 0; i < V; ++i) v += (d[i] - mu) * (d[i] - mu);
+      }
       const float r = rsqrtf(block_sum(v, red) * invW + a.eps);
-      for (int c = threadIdx.x; c < W; c += blockDim.x)
-        row[c] = fmaf(a.mult, fmaf((row[c] - mu) * r, a.pw[c], a.pb[c]), a.h_in[base + c]);
+      s = 0.f;
+      for (int c = c0; c < W; c += step) {
+        float d[V], g[V], b[V], h[V];
+        ln_ld<V>(row + c, d); ln_ld<V>(a.pw + c, g); ln_ld<V>(a.pb + c, b); ln_ld<V>(a.h_in + base + c, h);
+#pragma unroll
+        for (int i = 0; i < V; ++i) { d[i] = fmaf(a.mult, fmaf((d[i] - mu) * r, g[i], b[i]), h[i]); s += d[i]; }
+        ln_st<V>(row + c, d);
+      }
     } else {
-      for (int c = threadIdx.x; c < W; c += blockDim.x) row[c] = fmaf(a.mult, row[c], a.h_in[base + c]);
+      s = 0.f;
+      for (int c = c0; c < W; c += step) {
+        float d[V], h[V];
+        ln_ld<V>(row + c, d); ln_ld<V>(a.h_in + base + c, h);
+#pragma unroll
+        for (int i = 0; i < V; ++i) { d[i] = fmaf(a.mult, d[i], h[i]); s += d[i]; }
+        ln_st<V>(row + c, d);
+      }
     }
   } else {
-    for (int c = threadIdx.x; c < W; c += blockDim.x) row[c] = a.h_in[base + c];
+    for (int c = c0; c < W; c += step) {
+      float h[V];
+      ln_ld<V>(a.h_in + base + c, h);
+      ln_st<V>(row + c, h);
+#pragma unroll
+      for (int i = 0; i < V; ++i) s += h[i];
+    }
   }
-  float s = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) s += row[c];
   mean = block_sum(s, red) * invW;
   float v = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) { const float d = row[c] - mean; v += d * d; }
+  for (int c = c0; c < W; c += step) {
+    float d[V];
+    ln_ld<V>(row + c, d);
+#pragma unroll
+    for (int i = 0; i < V; ++i) v += (d[i] - mean) * (d[i] - mean);
+  }
   rstd = rsqrtf(block_sum(v, red) * invW + a.eps);
 }
 
-template <typename TO>
-__global__ void __launch_bounds__(LN_THREADS) add_layernorm_kernel(const LnArgs a) {
-  extern __shared__ float ln_smem[];
+// the lines of a vector that does not depend on the step before, asked for ahead of the wait for that step
+__device__ __forceinline__ void ln_prefetch(const float* p, int W) {
+  if (p)
+    for (int c = threadIdx.x * 32; c < W; c += blockDim.x * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + c));
+}
+
+template <typename TO, int V>
+__global__ void __launch_bounds__(1024) add_layernorm_kernel(const LnArgs a) {
+  extern __shared__ __align__(16) float ln_smem[];
   __shared__ float red[33];
+  const int W = a.W;
+  ln_prefetch(a.w, W); ln_prefetch(a.b, W); ln_prefetch(a.pw, W); ln_prefetch(a.pb, W); ln_prefetch(a.shift, W);
+  ln_prefetch(a.dbias, W);
   pdl_wait();
   pdl_trigger();
-  const int W = a.W;
+  const int c0 = threadIdx.x * V, step = blockDim.x * V;
   float* row = ln_smem;              // this block's row after the sum
   float* other = ln_smem + W;        // a neighbour's (only with a shift)
   const int r = blockIdx.x;
   const int t = a.rows ? a.rows[r] : r;
   float mean, rstd;
-  ln_row(a, t, row, red, mean, rstd);
-  if (a.h_out && a.delta)
-    for (int c = threadIdx.x; c < W; c += blockDim.x) a.h_out[(size_t)t * W + c] = row[c];
-  else if (a.h_out && a.h_out != a.h_in)
-    for (int c = threadIdx.x; c < W; c += blockDim.x) a.h_out[(size_t)t * W + c] = row[c];
+  ln_row<V>(a, t, row, red, mean, rstd);
+  if (a.h_out && (a.delta || a.h_out != a.h_in))
+    for (int c = c0; c < W; c += step) {
+      float d[V];
+      ln_ld<V>(row + c, d);
+      ln_st<V>(a.h_out + (size_t)t * W + c, d);
+    }
   TO* out = (TO*)a.out + (size_t)r * W;
   if (!a.shift) {
-    for (int c = threadIdx.x; c < W; c += blockDim.x) out[c] = from_f32<TO>(fmaf((row[c] - mean) * rstd, a.w[c], a.b[c]));
+    for (int c = c0; c < W; c += step) {
+      float d[V], g[V], b[V];
+      ln_ld<V>(row + c, d); ln_ld<V>(a.w + c, g); ln_ld<V>(a.b + c, b);
+#pragma unroll
+      for (int i = 0; i < V; ++i) d[i] = fmaf((d[i] - mean) * rstd, g[i], b[i]);
+      ln_st_out<V>(out + c, d);
+    }
     return;
   }
   const int s = a.seq_of_token[t];
@@ -94,24 +176,43 @@ __global__ void __launch_bounds__(LN_THREADS) add_layernorm_kernel(const LnArgs 
   float* st = a.state + (size_t)a.seq_slots[s] * W;
   if (t > t0) {
     float m2, r2;
-    ln_row(a, t - 1, other, red, m2, r2);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-      const float y = fmaf((row[c] - mean) * rstd, a.w[c], a.b[c]);
-      const float yp = fmaf((other[c] - m2) * r2, a.w[c], a.b[c]);
-      out[c] = from_f32<TO>(fmaf(yp - y, a.shift[c], y));
+    ln_row<V>(a, t - 1, other, red, m2, r2);
+    for (int c = c0; c < W; c += step) {
+      float d[V], o[V], g[V], b[V], sh[V];
+      ln_ld<V>(row + c, d); ln_ld<V>(other + c, o); ln_ld<V>(a.w + c, g); ln_ld<V>(a.b + c, b); ln_ld<V>(a.shift + c, sh);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float y = fmaf((d[i] - mean) * rstd, g[i], b[i]);
+        const float yp = fmaf((o[i] - m2) * r2, g[i], b[i]);
+        d[i] = fmaf(yp - y, sh[i], y);
+      }
+      ln_st_out<V>(out + c, d);
     }
     return;
   }
   // the first row a sequence brings: the row before it is the state, and this block leaves the new state
   const bool alone = t1 - t0 == 1;
   float m3 = 0.f, r3 = 0.f;
-  if (!alone) ln_row(a, t1 - 1, other, red, m3, r3);
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    const float y = fmaf((row[c] - mean) * rstd, a.w[c], a.b[c]);
-    const float yp = st[c];
-    out[c] = from_f32<TO>(fmaf(yp - y, a.shift[c], y));
-    st[c] = alone ? y : fmaf((other[c] - m3) * r3, a.w[c], a.b[c]);
+  if (!alone) ln_row<V>(a, t1 - 1, other, red, m3, r3);
+  for (int c = c0; c < W; c += step) {
+    float d[V], o[V], g[V], b[V], sh[V], yp[V], ns[V];
+    ln_ld<V>(row + c, d); ln_ld<V>(a.w + c, g); ln_ld<V>(a.b + c, b); ln_ld<V>(a.shift + c, sh); ln_ld<V>(st + c, yp);
+    if (!alone) ln_ld<V>(other + c, o);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float y = fmaf((d[i] - mean) * rstd, g[i], b[i]);
+      d[i] = fmaf(yp[i] - y, sh[i], y);
+      ns[i] = alone ? y : fmaf((o[i] - m3) * r3, g[i], b[i]);
+    }
+    ln_st_out<V>(out + c, d);
+    ln_st<V>(st + c, ns);
   }
+}
+
+template <typename TO, int V>
+static int ln_launch(const LnArgs& a, int R, int threads, size_t smem, cudaStream_t stream) {
+  if (smem > 48 * 1024) cudaFuncSetAttribute(add_layernorm_kernel<TO, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return sx_launch(add_layernorm_kernel<TO, V>, dim3(R), dim3(threads), smem, stream, a);
 }
 
 extern "C" int sx_add_layernorm(const float* h_in, float* h_out, const void* delta, int delta_dt, const float* dbias,
@@ -127,15 +228,15 @@ extern "C" int sx_add_layernorm(const float* h_in, float* h_out, const void* del
   a.h_in = h_in; a.h_out = h_out; a.delta = delta; a.delta_dt = delta_dt; a.dbias = dbias; a.pw = pw; a.pb = pb;
   a.mult = mult; a.w = w; a.b = b; a.eps = eps; a.out = out; a.rows = rows; a.shift = shift; a.state = state;
   a.seq_of_token = seq_of_token; a.cu_seqlens = cu_seqlens; a.seq_slots = seq_slots; a.W = W;
-  const int threads = W <= 128 ? 64 : (W <= 1024 ? 128 : LN_THREADS);
+  const bool vec = W % 4 == 0 && (((uintptr_t)h_in | (uintptr_t)h_out | (uintptr_t)delta | (uintptr_t)dbias | (uintptr_t)pw |
+                               (uintptr_t)pb | (uintptr_t)w | (uintptr_t)b | (uintptr_t)out | (uintptr_t)shift |
+                               (uintptr_t)state) & 15) == 0;
+  // a thread an element group where the rows are few (a row's loads all in flight at once), else 256 threads a row
+  const int groups = vec ? W / 4 : W;
+  int threads = R <= 64 ? groups : (groups < LN_THREADS ? groups : LN_THREADS);
+  threads = threads > 1024 ? 1024 : (threads + 31) / 32 * 32;
   const size_t smem = (size_t)W * sizeof(float) * (shift ? 2 : 1);
-  if (out_dt == SX_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(add_layernorm_kernel<float>, dim3(R), dim3(threads), smem, stream, a);
-  }
-  if (out_dt == SX_BF16) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(add_layernorm_kernel<bf16>, dim3(R), dim3(threads), smem, stream, a);
-  }
+  if (out_dt == SX_F32) return vec ? ln_launch<float, 4>(a, R, threads, smem, stream) : ln_launch<float, 1>(a, R, threads, smem, stream);
+  if (out_dt == SX_BF16) return vec ? ln_launch<bf16, 4>(a, R, threads, smem, stream) : ln_launch<bf16, 1>(a, R, threads, smem, stream);
   return SX_ERR_DTYPE;
 }

@@ -9,6 +9,7 @@ import numpy as np
 import torch
 
 from ._lib import KernelError, c_float, c_int, check, dt_code, fn, ptr, require_cuda, stream
+from .options import OPTIONS
 
 
 def heads_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor, k_pages: Optional[torch.Tensor],
@@ -45,6 +46,32 @@ def heads_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch
 
 
 SCORED_TILE_ROWS = 4
+TALK_TILE_ROWS = 8          # rows a block of the tensor-core kernel for sigmoid weights takes
+TALK_MAX_SMEM = 220 * 1024
+
+_TALK_SMEM = {}
+
+
+def talk_prefill_applies(H: int, G: int, dim: int, vdim: int, dtype, softmax: bool, dist_bias) -> bool:
+    """Whether prompt portions of this attention run on the tensor-core kernel: sigmoid weights, no distance table,
+    bfloat16, a shape it is built for, and a block's shared memory within the SM's."""
+    if softmax or dist_bias is not None or dtype != torch.bfloat16 or not OPTIONS.attn_scored_tc:
+        return False
+    key = (H, G, dim, vdim)
+    need = _TALK_SMEM.get(key)
+    if need is None:
+        f = fn("attn_scored", "sx_attn_talk_prefill_smem")
+        need = _TALK_SMEM[key] = int(f(c_int(H), c_int(G), c_int(dim), c_int(vdim)))
+    return 0 <= need <= TALK_MAX_SMEM
+
+
+def _tiles(ctx, rows: int, device):
+    tiles = ctx.scratch.get(("scored_tiles", rows))
+    if tiles is None:
+        a, b = scored_tiles(ctx.host["cu_seqlens"], rows)
+        both = torch.from_numpy(np.asarray([a, b], dtype=np.int32)).to(device, non_blocking=True)
+        tiles = ctx.scratch[("scored_tiles", rows)] = (both[0], both[1])
+    return tiles
 
 
 def scored_tiles(cu_seqlens, rows: int = SCORED_TILE_ROWS):
@@ -89,13 +116,16 @@ def attn_scored(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, c
         if n_chunks > 1:
             part = torch.empty((T, n_chunks, H, vdim), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((T, n_chunks, H, 2), dtype=torch.float32, device=q.device) if softmax else None
+    elif ctx.max_new >= TALK_TILE_ROWS and talk_prefill_applies(H, G, dim, vdim, q.dtype, softmax, dist_bias):
+        tok0, rows = _tiles(ctx, TALK_TILE_ROWS, q.device)
+        check(fn("attn_scored", "sx_attn_talk_prefill")(
+            ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table),
+            c_int(block_table.shape[1]), ptr(tok0), ptr(rows), c_int(tok0.numel()), c_int(H), c_int(G), c_int(dim),
+            c_int(vdim), c_float(scale), c_int(0 if not window else int(window)), ptr(talk), ptr(head_bias), ptr(gate),
+            c_int(out.shape[1]), stream()), "attn_talk_prefill")
+        return out
     elif ctx.max_new >= SCORED_TILE_ROWS:
-        tiles = ctx.scratch.get(("scored_tiles", SCORED_TILE_ROWS))
-        if tiles is None:
-            a, b = scored_tiles(ctx.host["cu_seqlens"])
-            both = torch.from_numpy(np.asarray([a, b], dtype=np.int32)).to(q.device, non_blocking=True)
-            tiles = ctx.scratch[("scored_tiles", SCORED_TILE_ROWS)] = (both[0], both[1])
-        tok0, rows = tiles
+        tok0, rows = _tiles(ctx, SCORED_TILE_ROWS, q.device)
         n_tiles, tq = tok0.numel(), SCORED_TILE_ROWS
     check(fn("attn_scored", "sx_attn_scored")(
         ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), ptr(part), ptr(part_ml), ptr(ctx.positions), ptr(ctx.seq_of_token),

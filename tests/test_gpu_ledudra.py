@@ -171,9 +171,12 @@ def _run_attention(q, k, v, H, G, D, Dv, scale, window, steps, dt, **kw):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,Dv,window", [(6, 2, 16, 12, 37), (8, 2, 64, 32, 136), (2, 2, 8, 40, None), (3, 1, 24, 10, 64),
-                                              (8, 1, 64, 64, 300), (1, 1, 32, 8, 1)])
+                                              (8, 1, 64, 64, 300), (1, 1, 32, 8, 1), (16, 4, 128, 64, 100), (32, 8, 64, 64, 37),
+                                              (8, 8, 128, 128, None), (16, 2, 64, 128, 70), (32, 4, 128, 128, 129)])
 def test_sigmoid_attention_with_scores_mixed_over_heads(H, G, D, Dv, window, dtype):
-    """A portion, then token by token (the keys cut into parts over the grid), and the whole sequence in portions of two."""
+    """A portion, then token by token (the keys cut into parts over the grid), the whole sequence in portions of two, and
+    portions whose lengths are no multiple of a block's rows.  (In bfloat16 the shapes of 8, 16 and 32 heads of size 64 or
+    128 run their portions on the tensor cores.)"""
     g = torch.Generator().manual_seed(H * D + Dv)
     T, cut = 330, 200
     edge = [cut - window, cut - window + 1] if window and window < cut else []
@@ -189,7 +192,8 @@ def test_sigmoid_attention_with_scores_mixed_over_heads(H, G, D, Dv, window, dty
     ref = ref * gate.double()[:, :, None]
     kw = dict(talk=talk.cuda(), head_bias=pb.cuda(), gate=gate.cuda())
     tol = dict(atol=1e-4, rtol=1e-4) if dtype == "float32" else dict(atol=6e-2, rtol=3e-2)
-    for steps in ([(0, cut)] + [(p, 1) for p in range(cut, T)], [(p, 2) for p in range(0, T, 2)], [(0, 3), (3, T - 3)]):
+    for steps in ([(0, cut)] + [(p, 1) for p in range(cut, T)], [(p, 2) for p in range(0, T, 2)], [(0, 3), (3, T - 3)],
+                  [(0, 13), (13, 99), (112, 9), (121, T - 121)]):
         got = _run_attention(q, k, v, H, G, D, Dv, scale, window, steps, dt, **kw)
         bad = (got.double() - ref).abs().amax(dim=(1, 2))
         assert torch.allclose(got.double(), ref, **tol), f"first wrong query {int((bad > tol['atol'] + tol['rtol'] * ref.abs().max()).nonzero()[0])}"
