@@ -224,6 +224,15 @@ __global__ void __launch_bounds__(SC_THREADS) attn_scored_kernel(const ScArgs a)
     const int j0 = tile << 5;
     const int page = bt[j0 >> 6];
     const int prow = j0 & 63;
+    if (TQ == 1) {
+      // a single token's step waits on memory: the tile's values are asked for now and come from L2 in part 3
+      const int lines = (vdim * (int)sizeof(T) + 127) >> 7;
+      for (int i = tid; i < G * SC_KT * lines; i += SC_THREADS) {
+        const int ln = i % lines, j = (i / lines) % SC_KT, c = i / (lines * SC_KT);
+        if (j0 + j <= last_pos && j0 + j >= lo)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(vp + (((size_t)page * G + c) * SX_PAGE + prow + j) * vdim + ln * (128 / sizeof(T))));
+      }
+    }
     // 1: raw scores of every head, a thread a (group of R heads, key)
     for (int it = tid; it < (H / R) * SC_KT; it += SC_THREADS) {
       const int hg = it >> 5, j = it & 31;
@@ -236,7 +245,7 @@ __global__ void __launch_bounds__(SC_THREADS) attn_scored_kernel(const ScArgs a)
       if (j0 + j <= last_pos) {
         const T* kr = kp + (((size_t)page * G + c) * SX_PAGE + prow + j) * dim;
         if (kvec) {
-#pragma unroll 4
+#pragma unroll 8
           for (int d = 0; d < dim; d += KV) {            // (unrolled: several 16-byte loads of the key in flight)
             float kf[KV];
             sc_io<T>::ld16(kr + d, kf);
@@ -383,25 +392,31 @@ __global__ void __launch_bounds__(128) attn_scored_merge_kernel(const float* __r
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x, h = blockIdx.y;
-  float m = -INFINITY;
-  if (softmax)
-    for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, part_ml[(((size_t)t * n_chunks + c) * H + h) * 2]);
+  __shared__ float fac[64];
+  __shared__ float red[33];
+  float inv_l = 1.f;
+  if (softmax) {
+    // the parts' factors exp(m_c - m) once, by the first threads (n_chunks <= 64 <= blockDim.x is not required)
+    float m = -INFINITY;
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) m = fmaxf(m, part_ml[(((size_t)t * n_chunks + c) * H + h) * 2]);
+    m = block_max(m, red);
+    float l = 0.f;
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+      const float* ml = part_ml + (((size_t)t * n_chunks + c) * H + h) * 2;
+      const float f = ml[0] == -INFINITY ? 0.f : expf(ml[0] - m);
+      fac[c] = f;
+      l = fmaf(f, ml[1], l);
+    }
+    l = block_sum(l, red);
+    inv_l = l > 0.f ? 1.f / l : 0.f;
+  }
   const float g = gate ? gate[(size_t)t * H + h] : 1.f;
   for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
-    const int i = h * vdim + d;
-    float o = 0.f, l = 0.f;
+    const float* p = part + (size_t)t * n_chunks * H * vdim + h * vdim + d;
+    float o = 0.f;
 #pragma unroll 16
-    for (int c = 0; c < n_chunks; ++c) {
-      float f = 1.f;
-      if (softmax) {
-        const float* ml = part_ml + (((size_t)t * n_chunks + c) * H + h) * 2;
-        f = ml[0] == -INFINITY ? 0.f : expf(ml[0] - m);
-        l = fmaf(f, ml[1], l);
-      }
-      o = fmaf(f, part[((size_t)t * n_chunks + c) * H * vdim + i], o);
-    }
-    if (softmax) o = l > 0.f ? o / l : 0.f;
-    out[(size_t)t * out_stride + i] = from_f32<T>(o * g);
+    for (int c = 0; c < n_chunks; ++c) o = fmaf(softmax ? fac[c] : 1.f, p[(size_t)c * H * vdim], o);
+    out[(size_t)t * out_stride + h * vdim + d] = from_f32<T>(o * inv_l * g);
   }
 }
 
@@ -443,6 +458,7 @@ extern "C" int sx_attn_scored(const void* q, const void* k_pages, const void* v_
   if ((tq != 1 && tq != 4) || (tile_tok0 == nullptr && tq != 1) || (n_chunks > 1 && (tq != 1 || tile_tok0 || !part)))
     return SX_ERR_SIZE;
   if (n_chunks > 1 && softmax && !part_ml) return SX_ERR_SIZE;
+  if (n_chunks > 64) return SX_ERR_SIZE;                       // the merge keeps a factor per part in shared memory
   if (dist_bias && dist_n <= 0) return SX_ERR_SIZE;
   ScArgs a;
   a.q = q; a.k_pages = k_pages; a.v_pages = v_pages; a.out = out; a.part = part; a.part_ml = part_ml;
@@ -474,7 +490,7 @@ extern "C" int sx_attn_scored(const void* q, const void* k_pages, const void* v_
 //   3  O^T_h [vdim x 8 queries] += V_kv(h)^T [vdim x 16 keys] P_h^T  (warp w: the same heads; the sums stay in registers,
 //      HPW * vdim / 4 of them a thread, which is what limits a block to 8 rows).
 // The next keys are fetched while the scores are mixed, the values while the raw scores are formed.
-// H = 8 * HPW heads exactly; DIM and VD are 64 or 128.
+// H = 8 * HPW heads exactly; DIM and VD are 32, 64 or 128.
 // =======================================================================================
 #include "attn_tile.cuh"
 
@@ -592,20 +608,37 @@ __global__ void __launch_bounds__(TK_THREADS, 1) attn_talk_prefill_kernel(const 
       float raw[H];
 #pragma unroll
       for (int gg = 0; gg < H; ++gg) raw[gg] = S[gg * (TK_KT * TK_TQ) + pair];
+      // four heads at a time: four independent chains of FFMA, their rows of the matrix loaded together
+      constexpr int HB = (H / 2) % 4 == 0 ? 4 : (H / 2) % 2 == 0 ? 2 : 1;
 #pragma unroll
-      for (int hh = 0; hh < H / 2; ++hh) {
-        const int h = half * (H / 2) + hh;
-        const float4* tr = reinterpret_cast<const float4*>(talk + h * H);
-        float acc = 0.f;
+      for (int hh = 0; hh < H / 2; hh += HB) {
+        const int h0 = half * (H / 2) + hh;
+        float acc[HB];
+#pragma unroll
+        for (int u = 0; u < HB; ++u) acc[u] = 0.f;
 #pragma unroll
         for (int g4 = 0; g4 < H / 4; ++g4) {
-          const float4 w4 = tr[g4];
-          acc = fmaf(w4.x, raw[4 * g4], acc); acc = fmaf(w4.y, raw[4 * g4 + 1], acc);
-          acc = fmaf(w4.z, raw[4 * g4 + 2], acc); acc = fmaf(w4.w, raw[4 * g4 + 3], acc);
+          float4 w4[HB];
+#pragma unroll
+          for (int u = 0; u < HB; ++u) w4[u] = reinterpret_cast<const float4*>(talk + (h0 + u) * H)[g4];
+#pragma unroll
+          for (int u = 0; u < HB; ++u) acc[u] = fmaf(w4[u].x, raw[4 * g4], acc[u]);
+#pragma unroll
+          for (int u = 0; u < HB; ++u) acc[u] = fmaf(w4[u].y, raw[4 * g4 + 1], acc[u]);
+#pragma unroll
+          for (int u = 0; u < HB; ++u) acc[u] = fmaf(w4[u].z, raw[4 * g4 + 2], acc[u]);
+#pragma unroll
+          for (int u = 0; u < HB; ++u) acc[u] = fmaf(w4[u].w, raw[4 * g4 + 3], acc[u]);
         }
-        if (a.head_bias) acc += a.head_bias[h];
-        const float w = vis ? sigmoid_acc(acc) : 0.f;
-        *reinterpret_cast<bf16*>(Ps + ((size_t)h * TK_TQ + qi) * L::PROW + key * 2) = __float2bfloat16_rn(w);
+#pragma unroll
+        for (int u = 0; u < HB; ++u) {
+          const int h = h0 + u;
+          if (a.head_bias) acc[u] += a.head_bias[h];
+          // the weight becomes a bfloat16 operand: the fast exponential's and division's few units in the last place of
+          // 32 bits are far below its rounding
+          const float w = vis ? __fdividef(1.f, 1.f + __expf(-acc[u])) : 0.f;
+          *reinterpret_cast<bf16*>(Ps + ((size_t)h * TK_TQ + qi) * L::PROW + key * 2) = __float2bfloat16_rn(w);
+        }
       }
     }
     cp_async_wait<1>();                                       // the values
@@ -662,18 +695,26 @@ static int talk_launch(const TkArgs& a, int n_tiles, cudaStream_t stream) {
   return sx_launch(attn_talk_prefill_kernel<HPW, DIM, VD>, dim3(n_tiles), dim3(TK_THREADS), smem, stream, a);
 }
 
+template <int HPW, int DIM>
+static int talk_pick_v(const TkArgs& a, int n_tiles, int vdim, cudaStream_t stream) {
+  if (vdim == 128) return talk_launch<HPW, DIM, 128>(a, n_tiles, stream);
+  if (vdim == 64) return talk_launch<HPW, DIM, 64>(a, n_tiles, stream);
+  if (vdim == 32) return talk_launch<HPW, DIM, 32>(a, n_tiles, stream);
+  return SX_ERR_SIZE;
+}
 template <int HPW>
 static int talk_pick(const TkArgs& a, int n_tiles, int dim, int vdim, cudaStream_t stream) {
-  if (dim == 128 && vdim == 128) return talk_launch<HPW, 128, 128>(a, n_tiles, stream);
-  if (dim == 64 && vdim == 64) return talk_launch<HPW, 64, 64>(a, n_tiles, stream);
-  if (dim == 128 && vdim == 64) return talk_launch<HPW, 128, 64>(a, n_tiles, stream);
-  if (dim == 64 && vdim == 128) return talk_launch<HPW, 64, 128>(a, n_tiles, stream);
+  if (dim == 128) return talk_pick_v<HPW, 128>(a, n_tiles, vdim, stream);
+  if (dim == 64) return talk_pick_v<HPW, 64>(a, n_tiles, vdim, stream);
+  if (dim == 32) return talk_pick_v<HPW, 32>(a, n_tiles, vdim, stream);
   return SX_ERR_SIZE;
 }
 
 // bytes of shared memory a block of the tensor-core prompt kernel needs, or -1 where it does not apply
 extern "C" int sx_attn_talk_prefill_smem(int H, int G, int dim, int vdim) {
-  if ((H != 8 && H != 16 && H != 32) || G <= 0 || H % G || (dim != 64 && dim != 128) || (vdim != 64 && vdim != 128)) return -1;
+  if ((H != 8 && H != 16 && H != 32) || G <= 0 || H % G || (dim != 32 && dim != 64 && dim != 128) ||
+      (vdim != 32 && vdim != 64 && vdim != 128))
+    return -1;
   const size_t row = (size_t)dim * 2 + 16, vrow = (size_t)vdim * 2 + 16;
   return (int)((size_t)H * TK_TQ * row + (size_t)H * TK_KT * TK_TQ * 4 + (size_t)H * TK_TQ * (TK_KT * 2 + 16) +
                      (size_t)H * H * 4 + (size_t)G * TK_KT * (row + vrow));

@@ -24,7 +24,7 @@ switches in its runtime options (crates/synaptix-config/src/runtime.rs, ``AttnBa
 ``attn_options_fast``  attention with capped scores, sinks or chunks of positions at head size 32 / 64 / 128 in
                     bfloat16 on the ``mma.sync`` kernels (else the plain kernel)
 ``attn_scored_tc``  prompt portions of the attention with sigmoid weights of scores mixed over the heads, in bfloat16
-                    at 8, 16 or 32 heads of size 64 / 128: products on ``mma.sync`` (else the all-FFMA kernel)
+                    at 8, 16 or 32 heads of size 32 / 64 / 128: products on ``mma.sync`` (else the all-FFMA kernel)
 ``pdl``             kernels are launched with programmatic dependent launch
 ``branch_streams``  single-token steps of a block whose mixer and feed-forward read the same stream: the feed-forward's
                     kernels run on a second CUDA stream beside the mixer's (inside a captured step: two branches of

@@ -172,10 +172,10 @@ def _run_attention(q, k, v, H, G, D, Dv, scale, window, steps, dt, **kw):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,Dv,window", [(6, 2, 16, 12, 37), (8, 2, 64, 32, 136), (2, 2, 8, 40, None), (3, 1, 24, 10, 64),
                                               (8, 1, 64, 64, 300), (1, 1, 32, 8, 1), (16, 4, 128, 64, 100), (32, 8, 64, 64, 37),
-                                              (8, 8, 128, 128, None), (16, 2, 64, 128, 70), (32, 4, 128, 128, 129)])
+                                              (8, 8, 128, 128, None), (16, 2, 64, 128, 70), (32, 4, 128, 128, 129), (8, 2, 32, 32, 50), (16, 16, 32, 64, 65)])
 def test_sigmoid_attention_with_scores_mixed_over_heads(H, G, D, Dv, window, dtype):
     """A portion, then token by token (the keys cut into parts over the grid), the whole sequence in portions of two, and
-    portions whose lengths are no multiple of a block's rows.  (In bfloat16 the shapes of 8, 16 and 32 heads of size 64 or
+    portions whose lengths are no multiple of a block's rows.  (In bfloat16 the shapes of 8, 16 and 32 heads of size 32, 64 or
     128 run their portions on the tensor cores.)"""
     g = torch.Generator().manual_seed(H * D + Dv)
     T, cut = 330, 200
