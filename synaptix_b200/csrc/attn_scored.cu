@@ -514,6 +514,7 @@ struct TkArgs {
   const int* tile_tok0; const int* tile_rows;
   int G; float scale; int window;
   const float* talk; const float* head_bias; const float* gate; int out_stride;
+  float* part; int n_chunks;      // n_chunks > 1: the keys in that many parts over blockIdx.y, sums to part [tokens, n_chunks, H, vdim]
 };
 
 // rows j0 .. j0+15 of every kv head's page -> dst [G][16][ROWB]; rows outside [lo, hi] are zero-filled
@@ -547,12 +548,23 @@ __global__ void __launch_bounds__(TK_THREADS, 1) attn_talk_prefill_kernel(const 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int tile = gridDim.x - 1 - blockIdx.x;               // late rows see the most keys: first
-  const int tok0 = a.tile_tok0[tile], rows = min(TK_TQ, a.tile_rows[tile]);
+  const int tok0 = a.tile_tok0 ? a.tile_tok0[tile] : tile;    // no tiles given: a block a token
+  const int rows = a.tile_tok0 ? min(TK_TQ, a.tile_rows[tile]) : 1;
   if (tid < TK_TQ) pos_q[tid] = tid < rows ? a.positions[tok0 + tid] : -1;
   const int first_pos = a.positions[tok0], last_pos = first_pos + rows - 1;
   const int lo = a.window > 0 ? max(0, first_pos - a.window + 1) : 0;
   const int* bt = a.block_table + (size_t)a.seq_of_token[tok0] * a.maxp;
-  const int j_begin = lo & ~(TK_KT - 1);
+  int j_begin = lo & ~(TK_KT - 1), j_end = last_pos + 1;       // this block's keys: j_begin <= j < j_end, 16 a turn
+  if (a.n_chunks > 1) {
+    const int turns = ((last_pos - j_begin) >> 4) + 1, per_chunk = (turns + a.n_chunks - 1) / a.n_chunks;
+    j_end = min(j_end, j_begin + ((int)blockIdx.y + 1) * per_chunk * TK_KT);
+    j_begin += (int)blockIdx.y * per_chunk * TK_KT;
+    if (j_begin >= j_end) {                                    // a part without keys adds nothing
+      for (int i = tid; i < rows * H * VD; i += TK_THREADS)
+        a.part[((size_t)(tok0 + i / (H * VD)) * a.n_chunks + blockIdx.y) * H * VD + i % (H * VD)] = 0.f;
+      return;
+    }
+  }
 
   // queries: [head][row][dim], rows beyond the tile zero
   for (int i = tid; i < H * TK_TQ * (DIM / 8); i += TK_THREADS) {
@@ -571,7 +583,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) attn_talk_prefill_kernel(const 
 #pragma unroll
     for (int n = 0; n < VD / 16; ++n) o[r][n][0] = o[r][n][1] = o[r][n][2] = o[r][n][3] = 0.f;
 
-  for (int j0 = j_begin; j0 <= last_pos; j0 += TK_KT) {
+  for (int j0 = j_begin; j0 < j_end; j0 += TK_KT) {
     tk_load<VD, L::VROW>(Vs, a.v_pages, bt[j0 >> 6], G, j0, lo, last_pos);
     cp_async_commit();
     cp_async_wait<1>();                                       // the keys (and, the first time, the queries)
@@ -597,7 +609,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) attn_talk_prefill_kernel(const 
       *reinterpret_cast<float2*>(sh + (g + 8) * TK_TQ + 2 * t) = make_float2(s[2] * a.scale, s[3] * a.scale);
     }
     __syncthreads();
-    if (j0 + TK_KT <= last_pos) tk_load<DIM, L::QROW>(Ks, a.k_pages, bt[(j0 + TK_KT) >> 6], G, j0 + TK_KT, lo, last_pos);
+    if (j0 + TK_KT < j_end) tk_load<DIM, L::QROW>(Ks, a.k_pages, bt[(j0 + TK_KT) >> 6], G, j0 + TK_KT, lo, last_pos);
     cp_async_commit();
     // 2: mixture over heads, bias, mask, sigmoid
     {
@@ -675,6 +687,15 @@ __global__ void __launch_bounds__(TK_THREADS, 1) attn_talk_prefill_kernel(const 
     for (int e = 0; e < 2; ++e) {
       const int qi = 2 * t + e;
       if (qi >= rows) continue;
+      if (a.n_chunks > 1) {                                   // (the gate is applied where the parts are added)
+        float* prow = a.part + ((size_t)(tok0 + qi) * a.n_chunks + blockIdx.y) * H * VD + (size_t)h * VD;
+#pragma unroll
+        for (int n = 0; n < VD / 16; ++n) {
+          prow[n * 16 + g] = o[r][n][e];
+          prow[n * 16 + g + 8] = o[r][n][2 + e];
+        }
+        continue;
+      }
       const float f = a.gate ? a.gate[(size_t)(tok0 + qi) * H + h] : 1.f;
       bf16* orow = a.out + (size_t)(tok0 + qi) * a.out_stride + (size_t)h * VD;
 #pragma unroll
@@ -692,7 +713,7 @@ static int talk_launch(const TkArgs& a, int n_tiles, cudaStream_t stream) {
   if (smem > 220 * 1024) return SX_ERR_SIZE;
   cudaError_t e = cudaFuncSetAttribute(attn_talk_prefill_kernel<HPW, DIM, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return sx_launch(attn_talk_prefill_kernel<HPW, DIM, VD>, dim3(n_tiles), dim3(TK_THREADS), smem, stream, a);
+  return sx_launch(attn_talk_prefill_kernel<HPW, DIM, VD>, dim3(n_tiles, a.n_chunks), dim3(TK_THREADS), smem, stream, a);
 }
 
 template <int HPW, int DIM>
@@ -720,21 +741,28 @@ extern "C" int sx_attn_talk_prefill_smem(int H, int G, int dim, int vdim) {
                      (size_t)H * H * 4 + (size_t)G * TK_KT * (row + vrow));
 }
 
-// tiles: up to 8 consecutive rows of one sequence each.  Sigmoid weights only; talk, head_bias and gate may be null.
+// tiles: up to 8 consecutive rows of one sequence each; tile_tok0 null: a tile a token (n_tiles tokens), and then the
+// keys may be cut into n_chunks <= 64 parts (part: float32 [tokens, n_chunks, H, vdim]) that a second kernel adds up.
+// Sigmoid weights only; talk, head_bias and gate may be null.
 extern "C" int sx_attn_talk_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* positions,
                                     const int* seq_of_token, const int* block_table, int maxp, const int* tile_tok0,
                                     const int* tile_rows, int n_tiles, int H, int G, int dim, int vdim, float scale, int window,
                                     const float* talk, const float* head_bias, const float* gate, int out_stride,
-                                    cudaStream_t stream) {
+                                    float* part, int n_chunks, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (sx_attn_talk_prefill_smem(H, G, dim, vdim) < 0 || out_stride < H * vdim || !tile_tok0 || !tile_rows) return SX_ERR_SIZE;
+  if (sx_attn_talk_prefill_smem(H, G, dim, vdim) < 0 || out_stride < H * vdim || (tile_tok0 == nullptr) != (tile_rows == nullptr))
+    return SX_ERR_SIZE;
+  if (n_chunks < 1 || n_chunks > 64 || (n_chunks > 1 && (tile_tok0 || !part))) return SX_ERR_SIZE;
   if (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return SX_ERR_ALIGN;
   TkArgs a;
   a.q = (const bf16*)q; a.k_pages = (const bf16*)k_pages; a.v_pages = (const bf16*)v_pages; a.out = (bf16*)out;
   a.positions = positions; a.seq_of_token = seq_of_token; a.block_table = block_table; a.maxp = maxp;
   a.tile_tok0 = tile_tok0; a.tile_rows = tile_rows; a.G = G; a.scale = scale; a.window = window; a.talk = talk;
-  a.head_bias = head_bias; a.gate = gate; a.out_stride = out_stride;
-  if (H == 32) return talk_pick<4>(a, n_tiles, dim, vdim, stream);
-  if (H == 16) return talk_pick<2>(a, n_tiles, dim, vdim, stream);
-  return talk_pick<1>(a, n_tiles, dim, vdim, stream);
+  a.head_bias = head_bias; a.gate = gate; a.out_stride = out_stride; a.part = part; a.n_chunks = n_chunks;
+  const int rc = H == 32 ? talk_pick<4>(a, n_tiles, dim, vdim, stream)
+               : H == 16 ? talk_pick<2>(a, n_tiles, dim, vdim, stream) : talk_pick<1>(a, n_tiles, dim, vdim, stream);
+  if (rc != 0 || n_chunks == 1) return rc;
+  const int mt = vdim <= 32 ? 32 : (vdim <= 64 ? 64 : 128);
+  return sx_launch(attn_scored_merge_kernel<bf16>, dim3(n_tiles, H), dim3(mt), 0, stream, (const float*)part, (const float*)nullptr,
+                   (bf16*)out, gate, H, vdim, n_chunks, 0, out_stride);
 }

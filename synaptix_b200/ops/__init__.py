@@ -293,14 +293,21 @@ def attn_scored(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, c
                 dist_bias=None, softmax: bool = False, gate=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention whose weights may depend on all heads' scores (see ``scored.attn_scored``).  Where every head stands
     alone (softmax, no mixture over heads, no gate), keys and values share one of the mma.sync kernels' head sizes and
-    the step brings portions of prompts, that kernel takes the step with the distance table as one of its options; a
-    number per head cancels in a softmax and is left out there."""
+    the step brings portions of prompts (or single tokens that see at most 1,024 keys), that kernel (its single-token
+    form) takes the step with the distance table as one of its options; a number per head cancels in a softmax and is
+    left out there."""
     if (softmax and talk is None and gate is None and out is None and vdim == dim and not ctx.all_single
             and ctx.host is not None and fast_supported(q.dtype, H, G, dim) and k_pages.dtype == q.dtype
             and OPTIONS.attn_options_fast and ctx.max_new >= 16):
         tiles = _query_tiles(ctx, 64, q.device)
         return attn_prefill_ex(q, k_pages, v_pages, tiles[0], tiles[1], ctx.cu_seqlens, ctx.seq_past, ctx.seq_lens,
                                block_table, H, G, dim, scale, window, dist=dist_bias)
+    if (softmax and talk is None and gate is None and out is None and vdim == dim and ctx.all_single
+            and ctx.n_seqs == q.shape[0] and fast_supported(q.dtype, H, G, dim) and k_pages.dtype == q.dtype
+            and OPTIONS.attn_options_fast and (min(ctx.max_len, window) if window else ctx.max_len) <= 1024):
+        # single tokens that see at most 16 pages: a block a (sequence, kv head) walks them (the options' form has no
+        # parts over the keys, so longer ranges stay with the all-heads kernel, which has)
+        return attn_decode_ex(q, k_pages, v_pages, ctx.seq_lens, block_table, H, G, dim, scale, window, dist=dist_bias)
     return attn_scored_all_heads(q, k_pages, v_pages, ctx, block_table, H, G, dim, vdim, scale, window, talk=talk,
                                  head_bias=head_bias, dist_bias=dist_bias, softmax=softmax, gate=gate, out=out)
 

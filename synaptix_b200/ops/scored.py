@@ -111,6 +111,18 @@ def attn_scored(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, c
         raise KernelError("attn_scored: the distance bias is float32 [H, n]")
     tok0 = rows = part = part_ml = None
     n_tiles, tq, n_chunks = T, 1, 1
+    if (ctx.all_single or ctx.host is None) and talk_prefill_applies(H, G, dim, vdim, q.dtype, softmax, dist_bias):
+        # single tokens on the tensor-core kernel: a block a (token, part of its keys), 16 keys a turn
+        keys = ctx.max_len if not window else min(ctx.max_len, window)
+        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+        n_chunks = max(1, min((2 * sms) // max(1, T), (keys + 15) // 16 + 1, 64))
+        part = torch.empty((T, n_chunks, H, vdim), dtype=torch.float32, device=q.device) if n_chunks > 1 else None
+        check(fn("attn_scored", "sx_attn_talk_prefill")(
+            ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table),
+            c_int(block_table.shape[1]), ptr(None), ptr(None), c_int(T), c_int(H), c_int(G), c_int(dim), c_int(vdim),
+            c_float(scale), c_int(0 if not window else int(window)), ptr(talk), ptr(head_bias), ptr(gate),
+            c_int(out.shape[1]), ptr(part), c_int(n_chunks), stream()), "attn_talk_prefill", launches=2 if n_chunks > 1 else 1)
+        return out
     if ctx.all_single or ctx.host is None:
         n_chunks = _chunks(T, ctx.max_len, window, q.device)
         if n_chunks > 1:
@@ -122,7 +134,7 @@ def attn_scored(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, c
             ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table),
             c_int(block_table.shape[1]), ptr(tok0), ptr(rows), c_int(tok0.numel()), c_int(H), c_int(G), c_int(dim),
             c_int(vdim), c_float(scale), c_int(0 if not window else int(window)), ptr(talk), ptr(head_bias), ptr(gate),
-            c_int(out.shape[1]), stream()), "attn_talk_prefill")
+            c_int(out.shape[1]), ptr(None), c_int(1), stream()), "attn_talk_prefill")
         return out
     elif ctx.max_new >= SCORED_TILE_ROWS:
         tok0, rows = _tiles(ctx, SCORED_TILE_ROWS, q.device)
