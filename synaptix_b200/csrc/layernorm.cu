@@ -64,9 +64,24 @@ template <int V> __device__ __forceinline__ void ln_ld_delta(const LnArgs& a, si
   }
 }
 
+// Block-wide sum with ONE barrier: every warp leaves its sum, and after the barrier every thread adds the warps' sums
+// in index order (the same number in every thread).  Two buffers in turn: a thread that writes a buffer again has passed
+// the barrier behind the other one, which every thread reaches only after reading this one.
+__device__ __forceinline__ float ln_sum(float v, float (*red)[32], int& turn) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  float* r = red[turn];
+  turn ^= 1;
+  if (lane == 0) r[warp] = v;
+  __syncthreads();
+  float s = 0.f;
+  for (int i = 0; i < nwarp; ++i) s += r[i];
+  return s;
+}
+
 // the row t after the sum, left in `row` (shared, W floats); returns mean and 1/sqrt(var + eps) of it
 template <int V>
-__device__ void ln_row(const LnArgs& a, int t, float* row, float* red, float& mean, float& rstd) {
+__device__ void ln_row(const LnArgs& a, int t, float* row, float (*red)[32], int& turn, float& mean, float& rstd) {
   const int W = a.W, c0 = threadIdx.x * V, step = blockDim.x * V;
   const float invW = 1.f / (float)W;
   const size_t base = (size_t)t * W;
@@ -85,7 +100,7 @@ __device__ void ln_row(const LnArgs& a, int t, float* row, float* red, float& me
       for (int i = 0; i < V; ++i) s += d[i];
     }
     if (a.pw) {
-      const float mu = block_sum(s, red) * invW;
+      const float mu = ln_sum(s, red, turn) * invW;
       float v = 0.f;
       for (int c = c0; c < W; c += step) {
         float d[V];
@@ -93,7 +108,7 @@ __device__ void ln_row(const LnArgs& a, int t, float* row, float* red, float& me
 #pragma unroll
         for (int i = 0; i < V; ++i) v += (d[i] - mu) * (d[i] - mu);
       }
-      const float r = rsqrtf(block_sum(v, red) * invW + a.eps);
+      const float r = rsqrtf(ln_sum(v, red, turn) * invW + a.eps);
       s = 0.f;
       for (int c = c0; c < W; c += step) {
         float d[V], g[V], b[V], h[V];
@@ -121,7 +136,7 @@ __device__ void ln_row(const LnArgs& a, int t, float* row, float* red, float& me
       for (int i = 0; i < V; ++i) s += h[i];
     }
   }
-  mean = block_sum(s, red) * invW;
+  mean = ln_sum(s, red, turn) * invW;
   float v = 0.f;
   for (int c = c0; c < W; c += step) {
     float d[V];
@@ -129,7 +144,7 @@ __device__ void ln_row(const LnArgs& a, int t, float* row, float* red, float& me
 #pragma unroll
     for (int i = 0; i < V; ++i) v += (d[i] - mean) * (d[i] - mean);
   }
-  rstd = rsqrtf(block_sum(v, red) * invW + a.eps);
+  rstd = rsqrtf(ln_sum(v, red, turn) * invW + a.eps);
 }
 
 // the lines of a vector that does not depend on the step before, asked for ahead of the wait for that step
@@ -141,7 +156,8 @@ __device__ __forceinline__ void ln_prefetch(const float* p, int W) {
 template <typename TO, int V>
 __global__ void __launch_bounds__(1024) add_layernorm_kernel(const LnArgs a) {
   extern __shared__ __align__(16) float ln_smem[];
-  __shared__ float red[33];
+  __shared__ float red[2][32];
+  int turn = 0;
   const int W = a.W;
   ln_prefetch(a.w, W); ln_prefetch(a.b, W); ln_prefetch(a.pw, W); ln_prefetch(a.pb, W); ln_prefetch(a.shift, W);
   ln_prefetch(a.dbias, W);
@@ -153,7 +169,7 @@ __global__ void __launch_bounds__(1024) add_layernorm_kernel(const LnArgs a) {
   const int r = blockIdx.x;
   const int t = a.rows ? a.rows[r] : r;
   float mean, rstd;
-  ln_row<V>(a, t, row, red, mean, rstd);
+  ln_row<V>(a, t, row, red, turn, mean, rstd);
   if (a.h_out && (a.delta || a.h_out != a.h_in))
     for (int c = c0; c < W; c += step) {
       float d[V];
@@ -176,7 +192,7 @@ __global__ void __launch_bounds__(1024) add_layernorm_kernel(const LnArgs a) {
   float* st = a.state + (size_t)a.seq_slots[s] * W;
   if (t > t0) {
     float m2, r2;
-    ln_row<V>(a, t - 1, other, red, m2, r2);
+    ln_row<V>(a, t - 1, other, red, turn, m2, r2);
     for (int c = c0; c < W; c += step) {
       float d[V], o[V], g[V], b[V], sh[V];
       ln_ld<V>(row + c, d); ln_ld<V>(other + c, o); ln_ld<V>(a.w + c, g); ln_ld<V>(a.b + c, b); ln_ld<V>(a.shift + c, sh);
@@ -193,7 +209,7 @@ __global__ void __launch_bounds__(1024) add_layernorm_kernel(const LnArgs a) {
   // the first row a sequence brings: the row before it is the state, and this block leaves the new state
   const bool alone = t1 - t0 == 1;
   float m3 = 0.f, r3 = 0.f;
-  if (!alone) ln_row<V>(a, t1 - 1, other, red, m3, r3);
+  if (!alone) ln_row<V>(a, t1 - 1, other, red, turn, m3, r3);
   for (int c = c0; c < W; c += step) {
     float d[V], o[V], g[V], b[V], sh[V], yp[V], ns[V];
     ln_ld<V>(row + c, d); ln_ld<V>(a.w + c, g); ln_ld<V>(a.b + c, b); ln_ld<V>(a.shift + c, sh); ln_ld<V>(st + c, yp);
