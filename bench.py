@@ -270,9 +270,9 @@ def ledudra_config(width, ff, nh, nkv, hd, rh, runs, vocab):
     distance table of 32 buckets up to 512 in the softmax layers, SwiGLU of ``ff`` everywhere."""
     common = dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, scale=hd ** -0.5, mask=dict(size=1000), v_mix=True)
     soft = dict(type="attention_2", mixer=dict(common, bias_max=512, bias_rows=32), mlp=dict(kind="dense", ff=ff))
-    sigm = dict(type="attention", mixer=dict(common, rot=dict(dims=hd // 2, base=1.0e6, scaling=dict(
-        factor=8.0, original=1024, fast=32.0, slow=1.0))), mlp=dict(kind="dense", ff=ff))
-    return dict(architecture="Ledudra", vocab=vocab, width=width, norm=dict(eps=1e-5), residual_mult=0.5,
+    sigm = dict(type="attention", mixer=dict(common, rot=dict(dims=hd // 2, base=5.0e5, scaling=dict(
+        factor=4.0, original=2048, fast=16.0, slow=2.0))), mlp=dict(kind="dense", ff=ff))
+    return dict(architecture="Ledudra", vocab=vocab, width=width, norm=dict(eps=1e-5), residual_mult=0.7,
                 layers=[(soft if i % 2 == 0 else sigm) for i in range(runs)])
 
 

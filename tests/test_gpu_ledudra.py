@@ -170,7 +170,7 @@ def _run_attention(q, k, v, H, G, D, Dv, scale, window, steps, dt, **kw):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,D,Dv,window", [(6, 2, 16, 12, 37), (8, 2, 64, 32, 136), (2, 2, 8, 40, None), (3, 1, 24, 10, 64),
+@pytest.mark.parametrize("H,G,D,Dv,window", [(6, 2, 16, 12, 37), (8, 4, 64, 32, 150), (2, 2, 8, 40, None), (3, 1, 24, 10, 64),
                                               (8, 1, 64, 64, 300), (1, 1, 32, 8, 1), (16, 4, 128, 64, 100), (32, 8, 64, 64, 37),
                                               (8, 8, 128, 128, None), (16, 2, 64, 128, 70), (32, 4, 128, 128, 129), (8, 2, 32, 32, 50), (16, 16, 32, 64, 65)])
 def test_sigmoid_attention_with_scores_mixed_over_heads(H, G, D, Dv, window, dtype):
@@ -200,7 +200,7 @@ def test_sigmoid_attention_with_scores_mixed_over_heads(H, G, D, Dv, window, dty
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,D,Dv,window,rows,far", [(4, 2, 8, 12, 70, 10, 50), (8, 2, 64, 32, 136, 16, 120), (3, 3, 16, 16, None, 2, 3),
+@pytest.mark.parametrize("H,G,D,Dv,window,rows,far", [(4, 2, 8, 12, 70, 10, 50), (8, 4, 64, 32, 150, 16, 100), (3, 3, 16, 16, None, 2, 3),
                                                        (2, 1, 24, 20, 9, 6, 7), (4, 1, 64, 64, 130, 32, 128), (6, 2, 32, 32, None, 12, 40),
                                                        (4, 2, 128, 128, 70, 8, 200), (16, 1, 64, 64, 64, 64, 65)])
 def test_softmax_attention_with_a_bias_per_distance_bucket(H, G, D, Dv, window, rows, far, dtype):

@@ -45,7 +45,7 @@ def test_rotation_of_pairs_keeps_relative_angles():
 def test_stretched_frequencies_of_the_package_equal_the_plain_ones():
     import numpy as np
     from synaptix_b200.parts import FrequencyRamp
-    for dims, base, sc in [(8, 1.0e4, dict(factor=4.0, original=64, fast=16.0, slow=2.0)), (32, 1.0e6, dict(factor=8.0, original=128, fast=32.0, slow=1.0)),
+    for dims, base, sc in [(8, 1.0e4, dict(factor=4.0, original=64, fast=16.0, slow=2.0)), (32, 5.0e5, dict(factor=6.0, original=128, fast=24.0, slow=1.5)),
                            (6, 100.0, dict(factor=2.0, original=16, fast=4.0, slow=1.0)), (64, 5.0e5, dict(factor=16.0, original=4096, fast=8.0, slow=0.5))]:
         ref, mag = PL.scaled_frequencies(dims, base, sc)
         ramp = FrequencyRamp(**sc)

@@ -46,9 +46,9 @@ LB = dict(architecture="Ledudra", vocab=131, width=64, norm=dict(eps=1e-6), resi
 LB_INIT = dict(seed=7, std_matrix=0.1, std_embedding=0.6, std_gain=0.2, std_bias=0.3)
 
 # head sizes of 64 for keys and values, four and eight query heads a kv head, a window of 130, a long distance table
-LF = dict(architecture="Ledudra", vocab=203, width=128, norm=dict(eps=1e-5), residual_mult=0.5,
+LF = dict(architecture="Ledudra", vocab=203, width=128, norm=dict(eps=1e-5), residual_mult=0.6,
           layers=[_att2(4, 1, 64, 64, 0.125, 130, True, 32, 128, ff=256),
-                  _att(8, 1, 64, 64, 0.11, 100, True, _yarn(32, 1.0e6, 8.0, 128, 32.0, 1.0), ff=128),
+                  _att(8, 1, 64, 64, 0.11, 100, True, _yarn(32, 5.0e5, 6.0, 128, 24.0, 1.5), ff=128),
                   _att2(4, 1, 32, 64, 0.2, 200, True, 16, 100, ff=128)])
 LF_INIT = dict(seed=11, std_matrix=0.06, std_embedding=0.5, std_gain=0.1, std_bias=0.3)
 
