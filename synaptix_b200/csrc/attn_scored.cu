@@ -30,7 +30,23 @@ struct PrepArgs {
   const float* inv_freq; int rot_dims; float mag;
   const float* v_first_in; float* v_first_out; const float* lam;
   float* gate_out; int n_gate;
+  int vec;        // every head is a multiple of four elements and every pointer 16-byte aligned: four elements a lane
 };
+
+__device__ __forceinline__ void prep_st4(float* p, float x, float y, float z, float w) {
+  *reinterpret_cast<float4*>(p) = make_float4(x, y, z, w);
+}
+__device__ __forceinline__ void prep_st4(bf16* p, float x, float y, float z, float w) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(x, y), hi = __floats2bfloat162_rn(z, w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+__device__ __forceinline__ float4 prep_ld4(const float* p, const float* b) {
+  float4 x = *reinterpret_cast<const float4*>(p);
+  if (b) { const float4 y = *reinterpret_cast<const float4*>(b); x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w; }
+  return x;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(128) heads_prepare_kernel(const PrepArgs a) {
@@ -61,6 +77,33 @@ __global__ void __launch_bounds__(128) heads_prepare_kernel(const PrepArgs a) {
         dst = (T*)a.k_pages + (((size_t)page * G + (head - H)) * SX_PAGE + (pos & 63)) * dim;
       }
       float inv = 1.f;
+      if (a.vec) {
+        // four elements a lane (two pairs of the rotation): 16-byte loads, 8- or 16-byte stores
+        if (gain) {
+          float ss = 0.f;
+          for (int d = lane * 4; d < dim; d += 128) {
+            const float4 x = prep_ld4(src + d, bs ? bs + d : nullptr);
+            ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+          }
+          inv = rsqrtf(warp_sum(ss) / (float)dim + a.eps);
+        }
+        for (int d = lane * 4; d < dim; d += 128) {
+          float4 x = prep_ld4(src + d, bs ? bs + d : nullptr);
+          if (gain) {
+            const float4 gn = *reinterpret_cast<const float4*>(gain + d);
+            x.x *= inv * gn.x; x.y *= inv * gn.y; x.z *= inv * gn.z; x.w *= inv * gn.w;
+          }
+          if (d < 2 * half) {
+            float s0, c0, s1, c1;
+            sincosf((float)pos * a.inv_freq[d >> 1], &s0, &c0);
+            sincosf((float)pos * a.inv_freq[(d >> 1) + 1], &s1, &c1);
+            s0 *= a.mag; c0 *= a.mag; s1 *= a.mag; c1 *= a.mag;
+            x = make_float4(x.x * c0 - x.y * s0, x.y * c0 + x.x * s0, x.z * c1 - x.w * s1, x.w * c1 + x.z * s1);
+          }
+          prep_st4(dst + d, x.x, x.y, x.z, x.w);
+        }
+        continue;
+      }
       if (gain) {
         float ss = 0.f;
         for (int d = lane; d < dim; d += 32) { const float x = src[d] + (bs ? bs[d] : 0.f); ss += x * x; }
@@ -85,6 +128,20 @@ __global__ void __launch_bounds__(128) heads_prepare_kernel(const PrepArgs a) {
       const int col = (H + G) * dim + c * vdim;
       const float* src = src_tok + col;
       T* dst = (a.v_pages && page_ok) ? (T*)a.v_pages + (((size_t)page * G + c) * SX_PAGE + (pos & 63)) * vdim : nullptr;
+      if (a.vec) {
+        for (int d = lane * 4; d < vdim; d += 128) {
+          float4 x = prep_ld4(src + d, a.bias ? a.bias + col + d : nullptr);
+          const size_t vi = ((size_t)t * G + c) * vdim + d;
+          if (a.v_first_in) {
+            const float4 f = *reinterpret_cast<const float4*>(a.v_first_in + vi);
+            x.x = (1.f - lam) * x.x + lam * f.x; x.y = (1.f - lam) * x.y + lam * f.y;
+            x.z = (1.f - lam) * x.z + lam * f.z; x.w = (1.f - lam) * x.w + lam * f.w;
+          }
+          if (a.v_first_out) *reinterpret_cast<float4*>(a.v_first_out + vi) = x;
+          if (dst) prep_st4(dst + d, x.x, x.y, x.z, x.w);
+        }
+        continue;
+      }
       for (int d = lane; d < vdim; d += 32) {
         float x = src[d] + (a.bias ? a.bias[col + d] : 0.f);
         const size_t vi = ((size_t)t * G + c) * vdim + d;
@@ -116,9 +173,13 @@ extern "C" int sx_heads_prepare(const float* proj, int row, const float* bias, v
   a.H = H; a.G = G; a.dim = dim; a.vdim = vdim; a.qn = qn; a.kn = kn; a.eps = eps; a.inv_freq = inv_freq;
   a.rot_dims = rot_dims; a.mag = mag; a.v_first_in = v_first_in; a.v_first_out = v_first_out; a.lam = lam;
   a.gate_out = gate_out; a.n_gate = n_gate;
-  // few tokens: a block for every four heads, so that a single token's heads spread over the GPU
+  a.vec = dim % 4 == 0 && vdim % 4 == 0 && rot_dims % 4 == 0 && row % 4 == 0 &&
+          (((uintptr_t)proj | (uintptr_t)bias | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)qn |
+            (uintptr_t)kn | (uintptr_t)v_first_in | (uintptr_t)v_first_out) & 15) == 0;
+  // few tokens: a block for every four heads, so that a single token's heads spread over the GPU; many tokens: up to
+  // four blocks a token, so that a warp walks a few heads one after the other, not a dozen
   const int groups = (H + 2 * G + 3) / 4;
-  const dim3 grid(n_tokens, n_tokens >= 1024 ? 1 : (groups > 65535 ? 65535 : groups));
+  const dim3 grid(n_tokens, n_tokens >= 1024 ? (groups < 4 ? groups : 4) : (groups > 65535 ? 65535 : groups));
   if (dt == SX_F32) return sx_launch(heads_prepare_kernel<float>, grid, dim3(128), 0, stream, a);
   if (dt == SX_BF16) return sx_launch(heads_prepare_kernel<bf16>, grid, dim3(128), 0, stream, a);
   return SX_ERR_DTYPE;
