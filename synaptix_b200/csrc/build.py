@@ -41,6 +41,8 @@ LIBRARIES: Dict[str, tuple] = {
     "sampling": ("sampling.cu", []),
     "sequence": ("sequence.cu", []),
     "parallel": ("parallel.cu", []),
+    "normed": ("normed.cu", []),
+    "convqk": ("convqk.cu", []),
     "layernorm": ("layernorm.cu", []),
     "attn_scored": ("attn_scored.cu", []),
     "mlstm": ("mlstm.cu", []),

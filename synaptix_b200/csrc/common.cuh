@@ -169,13 +169,22 @@ __device__ __forceinline__ float cluster_load_f32(const float* local, uint32_t r
 
 // ---------------------------------------------------------------------------------------
 // The gated activation that the products of a stacked [gate; up] matrix apply in their epilogues:
-//   limit <= 0:  silu(g) * u                                              (SwiGLU)
-//   limit >  0:  g' sigmoid(alpha g') (u' + 1),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
+//   form 0, limit <= 0:  silu(g) * u                                              (SwiGLU)
+//   form 0, limit >  0:  g' sigmoid(alpha g') (u' + 1),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
+//   form 1:              gelu_tanh(g) * u,  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 // The choice is a value of the library (sx_set_gate_act), read when a product is launched and handed to its kernel by
 // value, so a launch recorded into a CUDA graph keeps the activation it was recorded with.
 // ---------------------------------------------------------------------------------------
-struct GateAct { float alpha, limit; };
+#define SX_GATE_SIGMOID 0
+#define SX_GATE_GELU_TANH 1
+struct GateAct { float alpha, limit; int form; };
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+  // 1 + tanh(y) = 2 / (1 + exp(-2 y)): one exponential, no cancellation for large |y|
+  const float y = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return z / (1.f + __expf(-2.f * y));
+}
 __device__ __forceinline__ float gate_mul(float g, float u, const GateAct a) {
+  if (a.form == SX_GATE_GELU_TANH) return gelu_tanh_f32(g) * u;
   if (a.limit > 0.f) {
     g = fminf(g, a.limit);
     u = fminf(fmaxf(u, -a.limit), a.limit);
@@ -183,7 +192,7 @@ __device__ __forceinline__ float gate_mul(float g, float u, const GateAct a) {
   }
   return g / (1.f + __expf(-g)) * u;
 }
-static GateAct g_sx_gate = {0.f, 0.f};
-extern "C" void sx_set_gate_act(float alpha, float limit) { g_sx_gate.alpha = alpha; g_sx_gate.limit = limit; }
+static GateAct g_sx_gate = {0.f, 0.f, SX_GATE_SIGMOID};
+extern "C" void sx_set_gate_act(float alpha, float limit, int form) { g_sx_gate.alpha = alpha; g_sx_gate.limit = limit; g_sx_gate.form = form; }
 
 #define SX_PAGE 64

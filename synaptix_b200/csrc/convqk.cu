@@ -1,0 +1,137 @@
+// Head preparation of an attention whose queries and keys pass a short causal convolution over time and are normed over
+// the whole projection, and whose values are the convolved keys (sm_100a), float32 and bfloat16.
+//
+//   convqk_prepare  one block a token.  With u the projection's q and k columns (C = Cq + Ck channels) and taps
+//                   w [C, n]:  y_t[c] = sum_j w[c, j] u_(t - n + 1 + j)[c], the earlier rows taken from the step's own
+//                   tokens of the same sequence or, before the portion's start, from the sequence's history (its last
+//                   n - 1 projected rows, oldest first; zeros before position 0).
+//                   v = y's key channels as they are (the cache's V); q = rms_norm over ALL Cq channels times gq (out),
+//                   k = rms_norm over ALL Ck channels times gk (the cache's K).  32-bit sums and norms.
+//                   all_single: every sequence brings one token, and the block also moves its history on.
+//   convqk_history  otherwise a second launch moves the histories on (a block a sequence; a thread walks a channel's
+//                   rows oldest first, so it reads a row before it overwrites it).
+//   sigmoid_gate    y[t, c] *= sigmoid(proj[t, col + c])   (an output gate per element, in place)
+#include "common.cuh"
+
+template <typename T>
+__global__ void __launch_bounds__(256) convqk_prepare_kernel(
+    const T* __restrict__ proj, int row, int col_q, int col_k, int Cq, int Ck, int taps, const float* __restrict__ wq,
+    const float* __restrict__ wk, const float* __restrict__ gq, const float* __restrict__ gk, float eps, float* __restrict__ hist,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ seq_past,
+    const int* __restrict__ seq_slots, const int* __restrict__ block_table, int maxp, T* __restrict__ q_out,
+    T* __restrict__ k_pages, T* __restrict__ v_pages, int G, int D, int all_single) {
+  extern __shared__ __align__(16) float ys[];       // Cq + Ck convolved values
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int s = seq_of_token[t], pos = positions[t], past = seq_past[s];
+  const int C = Cq + Ck, P = taps - 1;
+  float* hs = hist + (size_t)seq_slots[s] * P * C;
+  float sq = 0.f, sk = 0.f;
+  for (int c = tid; c < C; c += 256) {
+    const bool is_q = c < Cq;
+    const int pc = is_q ? col_q + c : col_k + (c - Cq);
+    const float* w = is_q ? wq + (size_t)c * taps : wk + (size_t)(c - Cq) * taps;
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int p = pos - P + j;                    // the position this tap reads
+      if (p < 0) continue;
+      float u;
+      if (p >= past) u = to_f32(proj[(size_t)(t - (pos - p)) * row + pc]);
+      else u = hs[(size_t)(p - past + P) * C + c];
+      acc = fmaf(w[j], u, acc);
+    }
+    ys[c] = acc;
+    if (is_q) sq += acc * acc; else sk += acc * acc;
+    if (all_single && P > 0) {                      // this thread owns the channel's history: shift it by one
+      for (int i = 0; i + 1 < P; ++i) hs[(size_t)i * C + c] = hs[(size_t)(i + 1) * C + c];
+      hs[(size_t)(P - 1) * C + c] = to_f32(proj[(size_t)t * row + pc]);
+    }
+  }
+  sq = block_sum(sq, red);
+  sk = block_sum(sk, red);
+  const float rq = rsqrtf(sq / (float)Cq + eps), rk = rsqrtf(sk / (float)Ck + eps);
+  for (int c = tid; c < Cq; c += 256) q_out[(size_t)t * Cq + c] = from_f32<T>(ys[c] * rq * gq[c]);
+  if (k_pages == nullptr) return;
+  const int page = block_table[(size_t)s * maxp + (pos >> 6)];
+  for (int c = tid; c < Ck; c += 256) {
+    const int g = c / D, d = c - g * D;
+    const size_t at = (((size_t)page * G + g) * SX_PAGE + (pos & 63)) * D + d;
+    const float y = ys[Cq + c];
+    k_pages[at] = from_f32<T>(y * rk * gk[c]);
+    v_pages[at] = from_f32<T>(y);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) convqk_history_kernel(const T* __restrict__ proj, int row, int col_q, int col_k, int Cq, int Ck,
+                                                             int taps, float* __restrict__ hist, const int* __restrict__ cu_seqlens,
+                                                             const int* __restrict__ seq_slots) {
+  pdl_wait();
+  pdl_trigger();
+  const int s = blockIdx.x;
+  const int t0 = cu_seqlens[s], n = cu_seqlens[s + 1] - t0;
+  const int C = Cq + Ck, P = taps - 1;
+  if (n <= 0) return;
+  float* hs = hist + (size_t)seq_slots[s] * P * C;
+  for (int c = threadIdx.x; c < C; c += 256) {
+    const int pc = c < Cq ? col_q + c : col_k + (c - Cq);
+    for (int i = 0; i < P; ++i) {                   // new row i is row i + n of [old rows ++ the step's rows]
+      const int src = i + n;
+      hs[(size_t)i * C + c] = src < P ? hs[(size_t)src * C + c] : to_f32(proj[(size_t)(t0 + src - P) * row + pc]);
+    }
+  }
+}
+
+extern "C" int sx_convqk_prepare(const void* proj, int row, int col_q, int col_k, int Cq, int Ck, int taps, const float* wq,
+                                 const float* wk, const float* gq, const float* gk, float eps, float* hist, const int* positions,
+                                 const int* seq_of_token, const int* cu_seqlens, const int* seq_past, const int* seq_slots,
+                                 const int* block_table, int maxp, void* q_out, void* k_pages, void* v_pages, int G, int D,
+                                 int n_tokens, int n_seqs, int all_single, int dt, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (taps < 1 || Cq <= 0 || Ck <= 0 || G * D != Ck || col_q < 0 || col_k < 0 || col_q + Cq > row || col_k + Ck > row)
+    return SX_ERR_SIZE;
+  const size_t smem = (size_t)(Cq + Ck) * sizeof(float);
+  if (smem > 48 * 1024) return SX_ERR_SIZE;
+  int rc;
+  if (dt == SX_F32)
+    rc = sx_launch(convqk_prepare_kernel<float>, dim3(n_tokens), dim3(256), smem, stream, (const float*)proj, row, col_q, col_k, Cq,
+                   Ck, taps, wq, wk, gq, gk, eps, hist, positions, seq_of_token, seq_past, seq_slots, block_table, maxp,
+                   (float*)q_out, (float*)k_pages, (float*)v_pages, G, D, all_single);
+  else if (dt == SX_BF16)
+    rc = sx_launch(convqk_prepare_kernel<bf16>, dim3(n_tokens), dim3(256), smem, stream, (const bf16*)proj, row, col_q, col_k, Cq,
+                   Ck, taps, wq, wk, gq, gk, eps, hist, positions, seq_of_token, seq_past, seq_slots, block_table, maxp,
+                   (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, G, D, all_single);
+  else
+    return SX_ERR_DTYPE;
+  if (rc || all_single || taps == 1) return rc;
+  if (dt == SX_F32)
+    return sx_launch(convqk_history_kernel<float>, dim3(n_seqs), dim3(256), 0, stream, (const float*)proj, row, col_q, col_k, Cq, Ck,
+                     taps, hist, cu_seqlens, seq_slots);
+  return sx_launch(convqk_history_kernel<bf16>, dim3(n_seqs), dim3(256), 0, stream, (const bf16*)proj, row, col_q, col_k, Cq, Ck,
+                   taps, hist, cu_seqlens, seq_slots);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ y, const T* __restrict__ proj, int row, int col, int n, size_t total) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / n;
+  const int c = (int)(idx - t * n);
+  const float g = to_f32(proj[t * row + col + c]);
+  y[idx] = from_f32<T>(to_f32(y[idx]) / (1.f + expf(-g)));
+}
+
+extern "C" int sx_sigmoid_gate(void* y, const void* proj, int row, int col, int n, int n_tokens, int dt, cudaStream_t stream) {
+  const size_t total = (size_t)n_tokens * n;
+  if (total == 0) return 0;
+  if (col < 0 || col + n > row) return SX_ERR_SIZE;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dt == SX_F32) return sx_launch(sigmoid_gate_kernel<float>, grid, dim3(256), 0, stream, (float*)y, (const float*)proj, row, col, n, total);
+  if (dt == SX_BF16) return sx_launch(sigmoid_gate_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)y, (const bf16*)proj, row, col, n, total);
+  return SX_ERR_DTYPE;
+}

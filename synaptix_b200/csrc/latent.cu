@@ -18,7 +18,8 @@
 //   latent_output_kernel   one block a (tile of 8 tokens, head): the parts merged and divided, then
 //                          y[h Dv + j] = sigmoid(gate_h) * sum_r Wuv[h Dv + j, r] o'[h, r]
 // Rotation: dims elements, pair i at angle position * inv_freq[i]; pairs = 1: elements (2i, 2i + 1), pairs = 0:
-// elements (i, i + dims / 2); elements from dims on pass unchanged.
+// elements (i, i + dims / 2); elements from dims on pass unchanged.  `mag` multiplies cos and sin (1 for a plain rotation;
+// a stretched rotation scales both).
 #include "common.cuh"
 #include <math.h>
 
@@ -35,7 +36,7 @@ __device__ __forceinline__ void rot_pair_index(int i, int dims, int pairs, int& 
 template <typename T>
 __global__ void __launch_bounds__(LT_THREADS) latent_prepare_kernel(
     const T* __restrict__ proj, int row, int Rq, int col, int R, int Dr, const float* __restrict__ gq,
-    const float* __restrict__ gkv, float eps, const float* __restrict__ inv_freq, int dims, int pairs,
+    const float* __restrict__ gkv, float eps, const float* __restrict__ inv_freq, int dims, int pairs, float mag,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int maxp,
     T* __restrict__ k_pages, T* __restrict__ cq_out) {
   __shared__ float red[33];
@@ -43,11 +44,13 @@ __global__ void __launch_bounds__(LT_THREADS) latent_prepare_kernel(
   pdl_trigger();
   const int t = blockIdx.x, tid = threadIdx.x;
   const T* pr = proj + (size_t)t * row;
-  float ss = 0.f;
-  for (int i = tid; i < Rq; i += LT_THREADS) { const float v = to_f32(pr[i]); ss += v * v; }
-  ss = block_sum(ss, red);
-  float inv = rsqrtf(ss / (float)Rq + eps);
-  for (int i = tid; i < Rq; i += LT_THREADS) cq_out[(size_t)t * Rq + i] = from_f32<T>(to_f32(pr[i]) * inv * gq[i]);
+  float ss = 0.f, inv;
+  if (Rq > 0) {                  // a layer whose queries come straight from the projection has no query latent
+    for (int i = tid; i < Rq; i += LT_THREADS) { const float v = to_f32(pr[i]); ss += v * v; }
+    ss = block_sum(ss, red);
+    inv = rsqrtf(ss / (float)Rq + eps);
+    for (int i = tid; i < Rq; i += LT_THREADS) cq_out[(size_t)t * Rq + i] = from_f32<T>(to_f32(pr[i]) * inv * gq[i]);
+  }
   if (col < 0 || k_pages == nullptr) return;
   const int pos = positions[t];
   const int page = block_table[(size_t)seq_of_token[t] * maxp + (pos >> 6)];
@@ -63,6 +66,8 @@ __global__ void __launch_bounds__(LT_THREADS) latent_prepare_kernel(
     rot_pair_index(i, dims, pairs, ia, ib);
     float sn, cs;
     sincosf((float)pos * inv_freq[i], &sn, &cs);
+    sn *= mag;
+    cs *= mag;
     const float u = to_f32(rr[ia]), v = to_f32(rr[ib]);
     kr[R + ia] = from_f32<T>(u * cs - v * sn);
     kr[R + ib] = from_f32<T>(v * cs + u * sn);
@@ -71,31 +76,30 @@ __global__ void __launch_bounds__(LT_THREADS) latent_prepare_kernel(
 }
 
 extern "C" int sx_latent_prepare(const void* proj, int row, int Rq, int col, int R, int Dr, const float* gq, const float* gkv,
-                                 float eps, const float* inv_freq, int dims, int pairs, const int* positions,
+                                 float eps, const float* inv_freq, int dims, int pairs, float mag, const int* positions,
                                  const int* seq_of_token, const int* block_table, int maxp, void* k_pages, void* cq_out,
                                  int T, int dt, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (Rq <= 0 || dims < 0 || dims > Dr || (dims & 1) || (dims > 0 && inv_freq == nullptr)) return SX_ERR_SIZE;
+  if (Rq < 0 || (Rq > 0 && (gq == nullptr || cq_out == nullptr)) || dims < 0 || dims > Dr || (dims & 1) || (dims > 0 && inv_freq == nullptr)) return SX_ERR_SIZE;
   if (dt == SX_F32)
     return sx_launch(latent_prepare_kernel<float>, dim3(T), dim3(LT_THREADS), 0, stream, (const float*)proj, row, Rq, col, R, Dr,
-                     gq, gkv, eps, inv_freq, dims, pairs, positions, seq_of_token, block_table, maxp, (float*)k_pages, (float*)cq_out);
+                     gq, gkv, eps, inv_freq, dims, pairs, mag, positions, seq_of_token, block_table, maxp, (float*)k_pages, (float*)cq_out);
   if (dt == SX_BF16)
     return sx_launch(latent_prepare_kernel<bf16>, dim3(T), dim3(LT_THREADS), 0, stream, (const bf16*)proj, row, Rq, col, R, Dr,
-                     gq, gkv, eps, inv_freq, dims, pairs, positions, seq_of_token, block_table, maxp, (bf16*)k_pages, (bf16*)cq_out);
+                     gq, gkv, eps, inv_freq, dims, pairs, mag, positions, seq_of_token, block_table, maxp, (bf16*)k_pages, (bf16*)cq_out);
   return SX_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(LT_QTHREADS) latent_query_kernel(
-    const T* __restrict__ q, const T* __restrict__ wuk, int H, int D, int Dr, int R, const float* __restrict__ inv_freq,
-    int dims, int pairs, const int* __restrict__ positions, float* __restrict__ qa, int n_tokens) {
-  extern __shared__ float qs[];          // LT_TOKENS * D
+    const T* __restrict__ q, int QW, const T* __restrict__ wuk, int H, int D, int Dr, int R, const float* __restrict__ inv_freq,
+    int dims, int pairs, float mag, const int* __restrict__ positions, float* __restrict__ qa, int n_tokens) {
+  extern __shared__ float qs[];          // LT_TOKENS * D; QW: elements between two tokens' queries (>= H (D + Dr))
   pdl_wait();
   pdl_trigger();
   const int t0 = blockIdx.x * LT_TOKENS, h = blockIdx.y, tid = threadIdx.x;
   const int nt = min(LT_TOKENS, n_tokens - t0);
-  const int QW = H * (D + Dr);
   for (int i = tid; i < LT_TOKENS * D; i += LT_QTHREADS) {
     const int tt = i / D, d = i % D;
     qs[i] = tt < nt ? to_f32(q[(size_t)(t0 + tt) * QW + h * (D + Dr) + d]) : 0.f;
@@ -125,6 +129,8 @@ __global__ void __launch_bounds__(LT_QTHREADS) latent_query_kernel(
     const T* qr = q + (size_t)(t0 + tt) * QW + h * (D + Dr) + D;
     float sn, cs;
     sincosf((float)positions[t0 + tt] * inv_freq[p], &sn, &cs);
+    sn *= mag;
+    cs *= mag;
     const float u = to_f32(qr[ia]), v = to_f32(qr[ib]);
     float* o = qa + ((size_t)(t0 + tt) * H + h) * (R + Dr) + R;
     o[ia] = u * cs - v * sn;
@@ -137,19 +143,20 @@ __global__ void __launch_bounds__(LT_QTHREADS) latent_query_kernel(
   }
 }
 
-extern "C" int sx_latent_query(const void* q, const void* wuk, int H, int D, int Dr, int R, const float* inv_freq, int dims,
-                               int pairs, const int* positions, float* qa, int T, int dt, cudaStream_t stream) {
+extern "C" int sx_latent_query(const void* q, int q_ld, const void* wuk, int H, int D, int Dr, int R, const float* inv_freq, int dims,
+                               int pairs, float mag, const int* positions, float* qa, int T, int dt, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (q_ld < H * (D + Dr)) return SX_ERR_SIZE;
   if (H <= 0 || H > 65535 || D < 0 || R <= 0 || dims < 0 || dims > Dr || (dims & 1)) return SX_ERR_SIZE;
   const size_t smem = (size_t)LT_TOKENS * (D > 0 ? D : 1) * sizeof(float);
   if (smem > 48 * 1024) return SX_ERR_SIZE;
   dim3 grid((T + LT_TOKENS - 1) / LT_TOKENS, H, (R + LT_QTHREADS - 1) / LT_QTHREADS);
   if (dt == SX_F32)
-    return sx_launch(latent_query_kernel<float>, grid, dim3(LT_QTHREADS), smem, stream, (const float*)q, (const float*)wuk, H, D, Dr,
-                     R, inv_freq, dims, pairs, positions, qa, T);
+    return sx_launch(latent_query_kernel<float>, grid, dim3(LT_QTHREADS), smem, stream, (const float*)q, q_ld, (const float*)wuk, H, D, Dr,
+                     R, inv_freq, dims, pairs, mag, positions, qa, T);
   if (dt == SX_BF16)
-    return sx_launch(latent_query_kernel<bf16>, grid, dim3(LT_QTHREADS), smem, stream, (const bf16*)q, (const bf16*)wuk, H, D, Dr,
-                     R, inv_freq, dims, pairs, positions, qa, T);
+    return sx_launch(latent_query_kernel<bf16>, grid, dim3(LT_QTHREADS), smem, stream, (const bf16*)q, q_ld, (const bf16*)wuk, H, D, Dr,
+                     R, inv_freq, dims, pairs, mag, positions, qa, T);
   return SX_ERR_DTYPE;
 }
 
@@ -486,23 +493,34 @@ __global__ void latent_expand_kernel(const T* __restrict__ kv, const T* __restri
 }
 
 template <typename T>
-__global__ void latent_rotate_q_kernel(T* __restrict__ q, const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                       int dims, int pairs, int H, int D, int Dr) {
+__global__ void latent_rotate_q_kernel(const T* q, int q_ld, T* out, const int* __restrict__ positions,
+                                       const float* __restrict__ inv_freq, int dims, int pairs, float mag, int H, int D, int Dr) {
+  // out [T, H (D + Dr)] takes the queries with their rotated parts rotated; `q` (rows q_ld apart) may be `out` itself:
+  // a thread reads both elements of a pair before it writes them, and copies touch one element each
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x;
   const float pos = (float)positions[t];
-  const int half = dims / 2;
+  const int half = dims / 2, HD = D + Dr;
+  const T* qi = q + (size_t)t * q_ld;
+  T* qo = out + (size_t)t * H * HD;
+  if (qi != qo)
+    for (int i = threadIdx.x; i < H * HD; i += blockDim.x) {
+      const int d = i % HD;
+      if (d < D || d >= D + dims) qo[i] = qi[i];
+    }
   for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
     const int h = i / half, p = i % half;
     int ia, ib;
     rot_pair_index(p, dims, pairs, ia, ib);
-    T* qr = q + ((size_t)t * H + h) * (D + Dr) + D;
+    const T* qr = qi + h * HD + D;
     float sn, cs;
     sincosf(pos * inv_freq[p], &sn, &cs);
+    sn *= mag;
+    cs *= mag;
     const float u = to_f32(qr[ia]), v = to_f32(qr[ib]);
-    qr[ia] = from_f32<T>(u * cs - v * sn);
-    qr[ib] = from_f32<T>(v * cs + u * sn);
+    qo[h * HD + D + ia] = from_f32<T>(u * cs - v * sn);
+    qo[h * HD + D + ib] = from_f32<T>(v * cs + u * sn);
   }
 }
 
@@ -547,12 +565,12 @@ extern "C" int sx_latent_expand(const void* kv, const void* kr, const int* posit
   return SX_ERR_DTYPE;
 }
 
-extern "C" int sx_latent_rotate_q(void* q, const int* positions, const float* inv_freq, int dims, int pairs, int H, int D, int Dr,
-                                  int T, int dt, cudaStream_t stream) {
-  if (T <= 0 || dims <= 0) return 0;
-  if (dims > Dr || (dims & 1)) return SX_ERR_SIZE;
-  if (dt == SX_F32) return sx_launch(latent_rotate_q_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)q, positions, inv_freq, dims, pairs, H, D, Dr);
-  if (dt == SX_BF16) return sx_launch(latent_rotate_q_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)q, positions, inv_freq, dims, pairs, H, D, Dr);
+extern "C" int sx_latent_rotate_q(const void* q, int q_ld, void* out, const int* positions, const float* inv_freq, int dims, int pairs,
+                                  float mag, int H, int D, int Dr, int T, int dt, cudaStream_t stream) {
+  if (T <= 0 || (dims <= 0 && q == out)) return 0;
+  if (dims > Dr || (dims & 1) || dims < 0 || q_ld < H * (D + Dr)) return SX_ERR_SIZE;
+  if (dt == SX_F32) return sx_launch(latent_rotate_q_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)q, q_ld, (float*)out, positions, inv_freq, dims, pairs, mag, H, D, Dr);
+  if (dt == SX_BF16) return sx_launch(latent_rotate_q_kernel<bf16>, dim3(T), dim3(256), 0, stream, (const bf16*)q, q_ld, (bf16*)out, positions, inv_freq, dims, pairs, mag, H, D, Dr);
   return SX_ERR_DTYPE;
 }
 

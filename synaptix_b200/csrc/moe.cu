@@ -1,8 +1,9 @@
 // A mixture of gated feed-forward experts (sm_100a), float32 and bfloat16; router, softmax and weights are 32-bit.
 //
 //   moe_route_kernel   one block a token (four in prompt steps): logits z_e = Wr[e] . x in 32-bit (Wr float32, x widened), softmax over ALL
-//                      experts, the `top` largest scores (ties: the lower index), weights = score / (sum of the chosen
-//                      + sum_eps) * scale  -> ids [T, top], weights [T, top]
+//                      experts (or a sigmoid each), the `top` largest choice values (ties: the lower index; optionally
+//                      with a correction per expert and only within the best groups, see RouteMode), weights = score /
+//                      (sum of the chosen + sum_eps) * scale, or score * scale  -> ids [T, top], weights [T, top]
 //   moe_sort_kernel    one block: the T * top (token, choice) pairs sorted by expert: offsets [E + 1], order [T * top]
 //                      (sorted place -> pair), place [T * top] (pair -> sorted place).  The order inside an expert's
 //                      group is whatever the atomics give; no result depends on it (each row is computed alone).
@@ -20,14 +21,26 @@
 
 #define MOE_ROUTE_THREADS 512
 
+// How the router turns logits into choices and weights:
+//   sigmoid     0: scores = softmax over all experts; 1: scores = sigmoid(logit), each expert alone
+//   correction  float32 [E] or null: added to the scores for the CHOICE only (the weights use the scores without it)
+//   groups, keep  the experts form `groups` equal groups of neighbours; a group's value is the sum of its two largest
+//               choice values (of its one, if a group is one expert) and only experts of the `keep` best groups (ties:
+//               the lower group) can be chosen; groups <= 1: every expert can
+//   renorm      1: weights = score / (sum of the chosen scores + sum_eps) * scale; 0: weights = score * scale
+struct RouteMode { int sigmoid; const float* correction; int groups, keep, renorm; };
+
 // TB tokens a block: a warp reads an expert's router row once for all of them; warp i then chooses for token i
 template <typename T, int TB>
 __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n_tokens,
                                                                        int W, int E, int top, float scale, float sum_eps,
-                                                                       int* __restrict__ ids, float* __restrict__ weights) {
+                                                                       int* __restrict__ ids, float* __restrict__ weights,
+                                                                       const RouteMode mode) {
   extern __shared__ __align__(16) float sm[];
   float* xs = sm;                 // TB * W
-  float* zs = sm + TB * W;        // TB * E
+  float* zs = sm + TB * W;        // TB * E: scores
+  float* cs = zs + TB * E;        // TB * E: choice values
+  float* gs = cs + TB * E;        // TB * groups: the groups' values
   pdl_wait();
   pdl_trigger();
   const int t0 = blockIdx.x * TB, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -69,19 +82,48 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const T* _
   if (warp >= nt) return;
   const int t = t0 + warp;
   float* z = zs + warp * E;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - mx); z[e] = p; sum += p; }
-  sum = warp_sum(sum);
+  float* c = cs + warp * E;
+  float sum = 1.f;
+  if (mode.sigmoid) {
+    for (int e = lane; e < E; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - mx); z[e] = p; sum += p; }
+    sum = warp_sum(sum);
+  }
+  for (int e = lane; e < E; e += 32) c[e] = z[e] + (mode.correction ? mode.correction[e] : 0.f);
   __syncwarp();
+  if (mode.groups > 1) {
+    // a lane a group: the sum of its two largest choice values; then the `keep` best groups stay, by rank
+    float* g = gs + warp * mode.groups;
+    const int size = E / mode.groups;
+    for (int gi = lane; gi < mode.groups; gi += 32) {
+      float a = -INFINITY, b = -INFINITY;
+      for (int e = gi * size; e < (gi + 1) * size; ++e) {
+        const float v = c[e];
+        if (v > a) { b = a; a = v; } else if (v > b) b = v;
+      }
+      g[gi] = size > 1 ? a + b : a;
+    }
+    __syncwarp();
+    for (int gi = lane; gi < mode.groups; gi += 32) {
+      const float v = g[gi];
+      int rank = 0;                                  // how many groups come before this one
+      for (int o = 0; o < mode.groups; ++o) rank += (g[o] > v || (g[o] == v && o < gi)) ? 1 : 0;
+      if (rank >= mode.keep)
+        for (int e = gi * size; e < (gi + 1) * size; ++e) c[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
   float chosen_sum = 0.f;
   for (int j = 0; j < top; ++j) {
-    float best = -1.f;
+    float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float p = z[e];
+      const float p = c[e];
       if (p > best) { best = p; bi = e; }       // a lane walks upwards: the first of equals stays
     }
 #pragma unroll
@@ -90,41 +132,46 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const T* _
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
-    const float s = best / sum;
+    if (bi >= E) bi = 0;                           // nothing left to choose (NaN logits): keep the index in range
+    const float s = z[bi] / sum;
     chosen_sum += s;
     if (lane == 0) {
       ids[(size_t)t * top + j] = bi;
       weights[(size_t)t * top + j] = s;
-      z[bi] = -2.f;                             // taken
     }
     __syncwarp();
+    if (lane == 0) c[bi] = -INFINITY;              // taken
+    __syncwarp();
   }
-  const float f = scale / (chosen_sum + sum_eps);
+  const float f = mode.renorm ? scale / (chosen_sum + sum_eps) : scale;
   for (int j = lane; j < top; j += 32) weights[(size_t)t * top + j] *= f;
 }
 
 template <typename T, int TB>
 static int moe_route_launch(const void* x, const float* wr, int T_, int W, int E, int top, float scale, float sum_eps, int* ids,
-                            float* weights, cudaStream_t stream) {
-  const size_t smem = (size_t)TB * (W + E) * sizeof(float);
+                            float* weights, const RouteMode mode, cudaStream_t stream) {
+  const size_t smem = (size_t)TB * (W + 2 * E + (mode.groups > 1 ? mode.groups : 0)) * sizeof(float);
   if (smem > 160 * 1024) return SX_ERR_SIZE;
   if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<T, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   return sx_launch(moe_route_kernel<T, TB>, dim3((T_ + TB - 1) / TB), dim3(MOE_ROUTE_THREADS), smem, stream, (const T*)x, wr, T_, W, E,
-                   top, scale, sum_eps, ids, weights);
+                   top, scale, sum_eps, ids, weights, mode);
 }
 
 extern "C" int sx_moe_route(const void* x, const float* wr, int T, int W, int E, int top, float scale, float sum_eps,
-                            int* ids, float* weights, int dt, cudaStream_t stream) {
+                            int* ids, float* weights, int sigmoid, const float* correction, int groups, int keep, int renorm,
+                            int dt, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || W <= 0) return SX_ERR_SIZE;
+  if (groups > 1 && (E % groups || keep <= 0 || keep > groups || top > keep * (E / groups))) return SX_ERR_SIZE;
+  const RouteMode mode = {sigmoid, correction, groups, keep, renorm};
   // prompt steps: four tokens a block share every router row they read (where that fits shared memory)
-  const bool four = T >= 256 && (size_t)4 * (W + E) * sizeof(float) <= 160 * 1024;
+  const bool four = T >= 256 && (size_t)4 * (W + 2 * E + (groups > 1 ? groups : 0)) * sizeof(float) <= 160 * 1024;
   if (dt == SX_F32)
-    return four ? moe_route_launch<float, 4>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, stream)
-                : moe_route_launch<float, 1>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, stream);
+    return four ? moe_route_launch<float, 4>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, mode, stream)
+                : moe_route_launch<float, 1>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, mode, stream);
   if (dt == SX_BF16)
-    return four ? moe_route_launch<bf16, 4>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, stream)
-                : moe_route_launch<bf16, 1>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, stream);
+    return four ? moe_route_launch<bf16, 4>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, mode, stream)
+                : moe_route_launch<bf16, 1>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, mode, stream);
   return SX_ERR_DTYPE;
 }
 
@@ -164,12 +211,22 @@ extern "C" int sx_moe_sort(const int* ids, int n, int E, int* offsets, int* orde
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float moe_silu(float g) { return g / (1.f + expf(-g)); }
+// the experts' gated activation (the library's value, see common.cuh), with precise exponentials: this file also
+// serves the 32-bit path
+__device__ __forceinline__ float moe_gate(float g, float u, const GateAct a) {
+  if (a.form == SX_GATE_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  if (a.limit > 0.f) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.f + expf(-a.alpha * g)) * (u + 1.f);
+  }
+  return g / (1.f + expf(-g)) * u;
+}
 
 template <typename TA, typename TW, typename TC, bool GATE_UP>
 __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ Wt, TC* __restrict__ C,
                                                        const int* __restrict__ offsets, const int* __restrict__ order,
-                                                       int E, int N, int K, int top) {
+                                                       int E, int N, int K, int top, const GateAct act) {
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
@@ -240,7 +297,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < N) C[(size_t)(r0 + r) * N + n] = from_f32<TC>(GATE_UP ? moe_silu(acc[i][j]) * acu[i][j] : acc[i][j]);
+      if (n < N) C[(size_t)(r0 + r) * N + n] = from_f32<TC>(GATE_UP ? moe_gate(acc[i][j], acu[i][j], act) : acc[i][j]);
     }
   }
 }
@@ -289,7 +346,7 @@ __device__ __forceinline__ void mm_mma(float* c, const uint32_t* a, uint32_t b0,
 template <typename TC, bool GATE_UP, int BM>
 __global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ Wt, TC* __restrict__ C,
                                                       const int* __restrict__ offsets, const int* __restrict__ order,
-                                                      int E, int N, int K, int top) {
+                                                      int E, int N, int K, int top, const GateAct act) {
   using Sh = MmShape<BM>;
   constexpr int STAGES = Sh::STAGES, MI = Sh::MI, NT = Sh::NT;
   extern __shared__ __align__(16) unsigned char mm_smem[];
@@ -415,7 +472,7 @@ __global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
             const int n = n0 + wn * (NT / 2) * 8 + j * 8 + col_in + x;
-            if (n < N) crow[n] = from_f32<TC>(moe_silu(acc[mi][j][half * 2 + x]) * acc[mi][NT / 2 + j][half * 2 + x]);
+            if (n < N) crow[n] = from_f32<TC>(moe_gate(acc[mi][j][half * 2 + x], acc[mi][NT / 2 + j][half * 2 + x], act));
           }
       } else {
 #pragma unroll
@@ -444,7 +501,7 @@ static int moe_mma_launch(const void* A, const void* Wt, void* C, const int* off
   const int nout = GATE_UP ? MM_BN / 2 : MM_BN;
   dim3 grid((N + nout - 1) / nout, tiles);
   return sx_launch(moe_mma_kernel<TC, GATE_UP, BM>, grid, dim3(256), smem, stream, (const bf16*)A, (const bf16*)Wt, (TC*)C, offsets,
-                   order, E, N, K, top);
+                   order, E, N, K, top, g_sx_gate);
 }
 
 // up to this many (token, choice) rows a step, blocks of 16 rows with the deeper ring
@@ -467,7 +524,7 @@ extern "C" int sx_moe_gemm(const void* A, const void* Wt, void* C, const int* of
 #undef MM_GO
   }
   dim3 grid((N + 63) / 64, tiles);
-#define MOE_GO(TA, TC, GU) return sx_launch(moe_gemm_kernel<TA, TA, TC, GU>, grid, dim3(256), 0, stream, (const TA*)A, (const TA*)Wt, (TC*)C, offsets, order, E, N, K, top)
+#define MOE_GO(TA, TC, GU) return sx_launch(moe_gemm_kernel<TA, TA, TC, GU>, grid, dim3(256), 0, stream, (const TA*)A, (const TA*)Wt, (TC*)C, offsets, order, E, N, K, top, g_sx_gate)
   if (gate_up) {
     if (a_dt == SX_F32 && c_dt == SX_F32) MOE_GO(float, float, true);
     if (a_dt == SX_BF16 && c_dt == SX_BF16) MOE_GO(bf16, bf16, true);

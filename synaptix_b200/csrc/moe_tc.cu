@@ -27,7 +27,7 @@ template <bool GATE_UP>
 __global__ void __launch_bounds__(MT_THREADS, 1) moe_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ out, const int* __restrict__ offsets,
-                                                               int E, int N, int K, int* __restrict__ status) {
+                                                               int E, int N, int K, int* __restrict__ status, const GateAct act) {
   extern __shared__ unsigned char mt_smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(mt_smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + MT_STAGES * MT_STAGE_BYTES);   // full[S], empty[S], accum
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(MT_THREADS, 1) moe_tc_kernel(const __grid_cons
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float g = __uint_as_float(v[i]);
-            f[i] = g / (1.f + __expf(-g)) * __uint_as_float(u[i]);
+            f[i] = gate_mul(g, __uint_as_float(u[i]), act);
           }
           if (ncol == 32 && (N % 8) == 0) {
 #pragma unroll
@@ -220,7 +220,7 @@ extern "C" int sx_moe_tc(const void* A, const void* Wt, void* out, const int* of
       set = true;
     }
     return sx_launch(moe_tc_kernel<true>, dim3((N + MT_BN / 2 - 1) / (MT_BN / 2), tiles), dim3(MT_THREADS), smem, stream, ma, mw, out,
-                     offsets, E, N, K, status);
+                     offsets, E, N, K, status, g_sx_gate);
   }
   static bool set2 = false;
   if (!set2) {
@@ -229,5 +229,5 @@ extern "C" int sx_moe_tc(const void* A, const void* Wt, void* out, const int* of
     set2 = true;
   }
   return sx_launch(moe_tc_kernel<false>, dim3((N + MT_BN - 1) / MT_BN, tiles), dim3(MT_THREADS), smem, stream, ma, mw, out, offsets, E,
-                   N, K, status);
+                   N, K, status, g_sx_gate);
 }

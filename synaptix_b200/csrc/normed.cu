@@ -1,0 +1,148 @@
+// Branches that are normed on their way into the residual stream (sm_100a), float32 and bfloat16 branches, all sums
+// and norms 32-bit.  One block a row; the row stays in shared memory between its passes.
+//
+//   add_normed:   v   = a                                        (one term without a gain), or
+//                 v   = f * (rms_norm(a) ga + rms_norm(b) gb)     (one or two terms with gains: mixers side by side)
+//                 d   = gp ? rms_norm(v) gp : v                   (the branch's own norm)
+//                 acc = h ? h[t] + d : d;   if write_h: h[t] = acc
+//                 y[r] = go ? rms_norm(acc) go : acc              (the next reader's rows: a cast, or the final norm)
+//                 rms_norm(x) = x / sqrt(mean(x^2) + eps).  Rows: r = 0..R-1, t = rows ? rows[r] : r.
+//   embed_bigram: out[t] = E[id_t] + B[(prev_t * mp + id_t * mc) mod n], row n of B for a sequence's first token;
+//                 prev_t is the token before in the step, or, for a portion's first token, the sequence's state
+//                 (its last token), which the same block then moves on to the portion's last token.
+#include "common.cuh"
+
+__device__ __forceinline__ float ldf(const void* p, int dt, size_t i) {
+  return dt == SX_F32 ? ((const float*)p)[i] : __bfloat162float(((const bf16*)p)[i]);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256) add_normed_kernel(
+    float* __restrict__ h, const void* __restrict__ a, int a_dt, const float* __restrict__ ga,
+    const void* __restrict__ b, int b_dt, const float* __restrict__ gb, float factor, const float* __restrict__ gp,
+    const float* __restrict__ go, float eps, TO* __restrict__ y, const int* __restrict__ rows, int H, int write_h) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const int t = rows ? rows[r] : r;
+  const size_t base = (size_t)t * H;
+  const float inv_h = 1.f / (float)H;
+  float ssv = 0.f;
+  if (a == nullptr) {
+    for (int i = tid; i < H; i += 256) row[i] = 0.f;
+  } else if (ga == nullptr) {
+    for (int i = tid; i < H; i += 256) { const float v = ldf(a, a_dt, base + i); row[i] = v; ssv += v * v; }
+  } else {
+    float sa = 0.f, sb = 0.f;
+    for (int i = tid; i < H; i += 256) {
+      const float va = ldf(a, a_dt, base + i);
+      sa += va * va;
+      if (b) { const float vb = ldf(b, b_dt, base + i); sb += vb * vb; }
+    }
+    sa = block_sum(sa, red);
+    const float ra = rsqrtf(sa * inv_h + eps);
+    float rb = 0.f;
+    if (b) { sb = block_sum(sb, red); rb = rsqrtf(sb * inv_h + eps); }
+    for (int i = tid; i < H; i += 256) {
+      float v = ldf(a, a_dt, base + i) * ra * ga[i];
+      if (b) v += ldf(b, b_dt, base + i) * rb * gb[i];
+      v *= factor;
+      row[i] = v;
+      ssv += v * v;
+    }
+  }
+  float rv = 1.f;
+  if (gp) { ssv = block_sum(ssv, red); rv = rsqrtf(ssv * inv_h + eps); }
+  float ssq = 0.f;
+  for (int i = tid; i < H; i += 256) {           // a thread passes over the same elements in every loop: no barrier needed
+    float acc = gp ? row[i] * rv * gp[i] : row[i];
+    if (h) {
+      acc += h[base + i];
+      if (write_h) h[base + i] = acc;
+    }
+    row[i] = acc;
+    ssq += acc * acc;
+  }
+  if (y == nullptr) return;
+  TO* yr = y + (size_t)r * H;
+  if (go) {
+    ssq = block_sum(ssq, red);
+    const float ro = rsqrtf(ssq * inv_h + eps);
+    for (int i = tid; i < H; i += 256) yr[i] = from_f32<TO>(row[i] * ro * go[i]);
+  } else {
+    for (int i = tid; i < H; i += 256) yr[i] = from_f32<TO>(row[i]);
+  }
+}
+
+extern "C" int sx_add_normed(float* h, const void* a, int a_dt, const float* ga, const void* b, int b_dt, const float* gb,
+                             float factor, const float* gp, const float* go, float eps, void* y, int y_dt, const int* rows,
+                             int R, int H, int write_h, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (H <= 0 || (b != nullptr && (a == nullptr || ga == nullptr || gb == nullptr))) return SX_ERR_SIZE;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return SX_ERR_SIZE;
+  if (y == nullptr || y_dt == SX_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return sx_launch(add_normed_kernel<float>, dim3(R), dim3(256), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
+                     (float*)y, rows, H, write_h);
+  }
+  if (y_dt == SX_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return sx_launch(add_normed_kernel<bf16>, dim3(R), dim3(256), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
+                     (bf16*)y, rows, H, write_h);
+  }
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Only the block of a portion's first token touches its sequence's state: it reads the token before and then stores
+// the portion's last token, so no block reads what another writes.  An id outside the table gives zeros for that part.
+template <typename T>
+__global__ void __launch_bounds__(256) embed_bigram_kernel(
+    const T* __restrict__ table, const T* __restrict__ bigram, const int* __restrict__ ids, const int* __restrict__ positions,
+    const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
+    int* __restrict__ last_token, float* __restrict__ out, int H, int V, int buckets, int mul_prev, int mul_cur) {
+  __shared__ int s_prev;
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  if (threadIdx.x == 0) {
+    const int s = seq_of_token[t];
+    const int first = cu_seqlens[s];
+    int prev;
+    if (t == first) {
+      const int slot = seq_slots[s];
+      prev = last_token[slot];
+      last_token[slot] = ids[cu_seqlens[s + 1] - 1];
+    } else {
+      prev = ids[t - 1];
+    }
+    s_prev = positions[t] == 0 ? -1 : prev;
+  }
+  __syncthreads();
+  const int prev = s_prev;
+  const bool ok = id >= 0 && id < V;
+  long long rowb = buckets;                                   // a sequence's first token
+  if (prev >= 0) rowb = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+  const T* e = table + (size_t)(ok ? id : 0) * H;
+  const T* g = bigram + (size_t)rowb * H;
+  float* o = out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f32(e[i]) + to_f32(g[i]) : 0.f;
+}
+
+extern "C" int sx_embed_bigram(const void* table, const void* bigram, int dt, const int* ids, const int* positions,
+                               const int* seq_of_token, const int* cu_seqlens, const int* seq_slots, int* last_token, float* out,
+                               int n_tokens, int H, int V, int buckets, int mul_prev, int mul_cur, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (buckets <= 0 || mul_prev < 0 || mul_cur < 0) return SX_ERR_SIZE;
+  if (dt == SX_F32)
+    return sx_launch(embed_bigram_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)table, (const float*)bigram, ids,
+                     positions, seq_of_token, cu_seqlens, seq_slots, last_token, out, H, V, buckets, mul_prev, mul_cur);
+  if (dt == SX_BF16)
+    return sx_launch(embed_bigram_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)table, (const bf16*)bigram, ids,
+                     positions, seq_of_token, cu_seqlens, seq_slots, last_token, out, H, V, buckets, mul_prev, mul_cur);
+  return SX_ERR_DTYPE;
+}

@@ -883,23 +883,28 @@ extern "C" int sx_retention_any(const void* proj, int row, int q_off, int k_off,
 //   g = min(gu[t, i], limit),  u = clamp(gu[t, I + i], -limit, limit),  out = g * sigmoid(alpha g) * (u + 1)
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void capped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, float alpha, float limit, size_t n) {
+__global__ void capped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, float alpha, float limit, int form, size_t n) {
   pdl_wait();
   pdl_trigger();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n) return;
   const size_t t = idx / I;
   const int i = (int)(idx - t * I);
+  if (form == SX_GATE_GELU_TANH) {          // the tanh form of GELU of the gate, times up (precise functions: the 32-bit path)
+    const float z = to_f32(gu[t * 2 * I + i]), u = to_f32(gu[t * 2 * I + I + i]);
+    out[idx] = from_f32<T>(0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))) * u);
+    return;
+  }
   const float g = fminf(to_f32(gu[t * 2 * I + i]), limit);
   const float u = fminf(fmaxf(to_f32(gu[t * 2 * I + I + i]), -limit), limit);
   out[idx] = from_f32<T>(g * sigmoid_f32(alpha * g) * (u + 1.f));
 }
-extern "C" int sx_capped_glu(const void* gu, void* out, int n_tokens, int I, float alpha, float limit, int dt, cudaStream_t stream) {
+extern "C" int sx_capped_glu(const void* gu, void* out, int n_tokens, int I, float alpha, float limit, int form, int dt, cudaStream_t stream) {
   const size_t n = (size_t)n_tokens * I;
   if (n == 0) return 0;
   const dim3 grid((unsigned)((n + 255) / 256));
-  if (dt == SX_F32) return sx_launch(capped_glu_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, (float*)out, I, alpha, limit, n);
-  if (dt == SX_BF16) return sx_launch(capped_glu_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, I, alpha, limit, n);
+  if (dt == SX_F32) return sx_launch(capped_glu_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, (float*)out, I, alpha, limit, form, n);
+  if (dt == SX_BF16) return sx_launch(capped_glu_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, I, alpha, limit, form, n);
   return SX_ERR_DTYPE;
 }
 

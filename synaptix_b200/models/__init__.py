@@ -10,6 +10,7 @@ from . import qwen3 as _qwen3  # registers the architecture
 from . import vemedra as _vemedra  # registers the architecture
 from . import pidutar as _pidutar  # registers the architecture
 from . import ledudra as _ledudra  # registers the architecture
+from . import tamovik as _tamovik  # registers the architecture
 from .decoder import DecoderModel, Inject, LayerRun, StreamVectors
 
 __all__ = ["DecoderModel", "Inject", "LayerRun", "StreamVectors", "model_skeleton", "load_model", "parse_dtype"]

@@ -1,6 +1,7 @@
 """A decoder model as data: parts, and the order in which layers run.
 
-``layers`` are blocks; ``schedule`` lists the runs of a step in order.  A run
+``layers`` are blocks; ``schedule`` lists the runs of a step in order.  An embedding that carries a state per
+sequence (``cache_request`` / ``forward_step``) gets a cache entry of its own behind the layers' entries.  A run
 names a layer and the cache entry it works on, so a schedule may run a layer
 twice (two runs, each with a cache entry of its own) or let a layer read the
 cache another layer wrote (``write_cache=False`` and that layer's entry).  The
@@ -91,6 +92,10 @@ class DecoderModel(Part):
             if owners[r.cache_entry] is None:
                 raise ValueError(f"cache entry {r.cache_entry} is read but never written")
         self._entry_owner = owners
+        # an embedding with a state of its own (the token before) gets the cache entry behind the layers' entries
+        self._embedding_entry = n_entries if getattr(embedding, "cache_request", None) is not None else None
+        if self._embedding_entry is not None and self._keeps_embedding:
+            raise ValueError("a schedule that adds the embedding again needs an embedding without a state")
 
     @property
     def vocab_size(self) -> int:
@@ -105,7 +110,10 @@ class DecoderModel(Part):
 
     def cache_requests(self) -> List[CacheRequest]:
         """One request per cache entry, asked of the layer that writes it."""
-        return [self.layers[o].cache_request() for o in self._entry_owner]
+        requests = [self.layers[o].cache_request() for o in self._entry_owner]
+        if self._embedding_entry is not None:
+            requests.append(self.embedding.cache_request())
+        return requests
 
     # -- weights -----------------------------------------------------------
     def load(self, source: WeightSource, rt: Runtime, where: str = "weights") -> "DecoderModel":
@@ -117,7 +125,10 @@ class DecoderModel(Part):
     # -- one step ------------------------------------------------------------
     def forward(self, ctx: StepContext, cache) -> torch.Tensor:
         """Logits float32 ``[n_want, vocab]`` for ``ctx.want_rows``."""
-        h = self.embedding.forward(ctx.token_ids)
+        if self._embedding_entry is not None:
+            h = self.embedding.forward_step(ctx, cache.view(self._embedding_entry))
+        else:
+            h = self.embedding.forward(ctx.token_ids)
         h0 = self.embedding.forward(ctx.token_ids) if self._keeps_embedding else None     # h is summed into in place
         pending = None
         observe = getattr(ctx, "observe", None)

@@ -25,6 +25,8 @@ from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, e
 from .sequence import add_rmsnorm_conv, capped_glu, mingru, retention, stream_add
 from .block import add_scaled, add_scaled_rmsnorm, scale_rows
 from .layernorm import add_layernorm
+from .normed import add_normed, embed_bigram
+from .convqk import convqk_prepare, sigmoid_gate
 from .scored import attn_scored as attn_scored_all_heads, heads_prepare
 from .latent import (head_gate, latent_attention, latent_expand, latent_gather, latent_output, latent_prepare, latent_query,
                      latent_rotate_q)
@@ -36,7 +38,7 @@ __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavail
            "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
            "linear_into_residual", "linear_scaled", "projection_prepares_heads", "project_and_prepare", "rope_table",
            "add_rmsnorm_conv", "capped_glu", "mingru", "retention", "stream_add", "gate_activation",
-           "add_scaled", "add_scaled_rmsnorm", "scale_rows", "add_layernorm", "attn_scored", "heads_prepare", "latent_attention", "latent_output", "latent_prepare",
+           "add_normed", "embed_bigram", "convqk_prepare", "sigmoid_gate", "add_scaled", "add_scaled_rmsnorm", "scale_rows", "add_layernorm", "attn_scored", "heads_prepare", "latent_attention", "latent_output", "latent_prepare",
            "latent_query", "latent_gather", "latent_expand", "latent_rotate_q", "head_gate", "mlstm", "ExpertPlan", "moe_combine", "moe_down", "moe_gate_up", "moe_route", "moe_sort"]
 
 
@@ -156,8 +158,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             return gemm_tc(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
     y = gemm_generic(x, w, out_dtype=out_dtype if epilogue is None else x.dtype)
     if epilogue == "silu_mul":
-        alpha, limit = current_gate()            # which gated activation the epilogue stands for (see gate_activation)
-        y = capped_glu(y, alpha, limit) if limit > 0 else silu_mul(y)
+        alpha, limit, form = current_gate()      # which gated activation the epilogue stands for (see gate_activation)
+        y = capped_glu(y, alpha, limit, form) if (limit > 0 or form != 0) else silu_mul(y)
     return y
 
 

@@ -127,18 +127,20 @@ c_ulonglong = ctypes.c_ulonglong
 
 # ---------------------------------------------------------------------------------------------------------------
 # The gated activation of the products' "silu_mul" epilogue.  (0, 0) is silu(g) * u; (alpha, limit) with limit > 0 is
-# g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).  A feed-forward that wants the
-# second form runs its gate/up product inside ``gate_activation(alpha, limit)``; the faces of the products call
-# ``use_gate`` before a launch with that epilogue, which tells the library if its last value was another one.
+# g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit); ``form="gelu_tanh"`` is
+# gelu_tanh(g) * u (the tanh form of GELU; alpha and limit unused).  A feed-forward that wants another form than the
+# first runs its gate/up product inside ``gate_activation(...)``; the faces of the products call ``use_gate`` before a
+# launch with that epilogue, which tells the library if its last value was another one.
 # ---------------------------------------------------------------------------------------------------------------
-_GATE = [(0.0, 0.0)]
+GATE_FORMS = {"sigmoid": 0, "gelu_tanh": 1}
+_GATE = [(0.0, 0.0, 0)]
 _LIB_GATE = {}
 
 
 @contextlib.contextmanager
-def gate_activation(alpha: float, limit: float):
+def gate_activation(alpha: float = 0.0, limit: float = 0.0, form: str = "sigmoid"):
     old = _GATE[0]
-    _GATE[0] = (float(alpha), float(limit))
+    _GATE[0] = (float(alpha), float(limit), GATE_FORMS[form])
     try:
         yield
     finally:
@@ -146,6 +148,7 @@ def gate_activation(alpha: float, limit: float):
 
 
 def current_gate():
+    """``(alpha, limit, form code)`` of the gated activation in force."""
     return _GATE[0]
 
 
@@ -154,5 +157,5 @@ def use_gate(lib: str) -> None:
     if _LIB_GATE.get(lib) != want:
         f = getattr(_library(lib), "sx_set_gate_act")
         f.restype = None
-        f(ctypes.c_float(want[0]), ctypes.c_float(want[1]))
+        f(ctypes.c_float(want[0]), ctypes.c_float(want[1]), ctypes.c_int(want[2]))
         _LIB_GATE[lib] = want

@@ -10,13 +10,14 @@ import torch
 from ._lib import KernelError, c_float, c_int, check, dt_code, fn, ptr, require_cuda, stream
 
 
-def latent_prepare(proj: torch.Tensor, q_rank: int, col_kv: int, kv_rank: int, rot_dim: int, gain_q: torch.Tensor,
+def latent_prepare(proj: torch.Tensor, q_rank: int, col_kv: int, kv_rank: int, rot_dim: int, gain_q: Optional[torch.Tensor],
                    gain_kv: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int, pairs: bool,
-                   ctx, block_table: torch.Tensor, k_pages: Optional[torch.Tensor]) -> torch.Tensor:
+                   ctx, block_table: torch.Tensor, k_pages: Optional[torch.Tensor], magnitude: float = 1.0) -> Optional[torch.Tensor]:
     """From the stacked input projection ``proj [T, row]``: the normed query latent ``rmsnorm(proj[:, :q_rank]) * gain_q``
-    (returned, ``proj``'s dtype) and, if ``k_pages`` is given, the token's cache row: ``rmsnorm(proj[:, col_kv : col_kv +
-    kv_rank]) * gain_kv`` and behind it the next ``rot_dim`` columns with their first ``rot_dims`` elements rotated
-    (``pairs``: neighbouring elements paired, else element ``i`` with ``i + rot_dims / 2``)."""
+    (returned, ``proj``'s dtype; ``q_rank = 0``: there is none and ``None`` is returned) and, if ``k_pages`` is given,
+    the token's cache row: ``rmsnorm(proj[:, col_kv : col_kv + kv_rank]) * gain_kv`` and behind it the next ``rot_dim``
+    columns with their first ``rot_dims`` elements rotated (``pairs``: neighbouring elements paired, else element ``i``
+    with ``i + rot_dims / 2``; cos and sin times ``magnitude``)."""
     require_cuda(proj, gain_q, gain_kv, inv_freq, block_table, k_pages)
     T, row = proj.shape
     if k_pages is not None:
@@ -24,29 +25,32 @@ def latent_prepare(proj: torch.Tensor, q_rank: int, col_kv: int, kv_rank: int, r
             raise KernelError("latent_prepare: the key/value latent's columns do not fit")
         if k_pages.dtype != proj.dtype or k_pages.dim() != 4 or tuple(k_pages.shape[1:]) != (1, 64, kv_rank + rot_dim):
             raise KernelError("latent_prepare: cache pages must be [n_pages, 1, 64, kv_rank + rot_dim] of the compute dtype")
-    if q_rank > row or gain_q.numel() != q_rank:
+    if q_rank > row or (q_rank > 0 and (gain_q is None or gain_q.numel() != q_rank)):
         raise KernelError("latent_prepare: the query latent does not fit")
-    cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device)
+    if q_rank == 0 and k_pages is None:
+        return None
+    cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device) if q_rank > 0 else None
     check(fn("latent", "sx_latent_prepare")(
         ptr(proj), c_int(row), c_int(q_rank), c_int(col_kv if k_pages is not None else -1), c_int(kv_rank), c_int(rot_dim),
         ptr(gain_q), ptr(gain_kv), c_float(eps), ptr(inv_freq), c_int(rot_dims if inv_freq is not None else 0),
-        c_int(1 if pairs else 0), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table), c_int(block_table.shape[1]),
-        ptr(k_pages), ptr(cq), c_int(T), c_int(dt_code(proj.dtype)), stream()), "latent_prepare")
+        c_int(1 if pairs else 0), c_float(magnitude), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table),
+        c_int(block_table.shape[1]), ptr(k_pages), ptr(cq), c_int(T), c_int(dt_code(proj.dtype)), stream()), "latent_prepare")
     return cq
 
 
 def latent_query(q: torch.Tensor, wuk: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int,
-                 inv_freq: Optional[torch.Tensor], rot_dims: int, pairs: bool, ctx) -> torch.Tensor:
-    """Queries ``q [T, heads * (dim + rot_dim)]`` taken into the latent's space: per head
-    ``[Wuk_h^T q_h | rotate(q_rot_h)]`` with ``wuk [heads * dim, kv_rank]``; float32 ``[T, heads, kv_rank + rot_dim]``."""
+                 inv_freq: Optional[torch.Tensor], rot_dims: int, pairs: bool, ctx, magnitude: float = 1.0) -> torch.Tensor:
+    """Queries (the first ``heads * (dim + rot_dim)`` columns of ``q``, which may be a wider stacked projection) taken into
+    the latent's space: per head ``[Wuk_h^T q_h | rotate(q_rot_h)]`` with ``wuk [heads * dim, kv_rank]``; float32
+    ``[T, heads, kv_rank + rot_dim]``."""
     require_cuda(q, wuk, inv_freq)
     T = q.shape[0]
-    if q.shape[1] != heads * (dim + rot_dim) or tuple(wuk.shape) != (heads * dim, kv_rank) or wuk.dtype != q.dtype:
+    if q.shape[1] < heads * (dim + rot_dim) or tuple(wuk.shape) != (heads * dim, kv_rank) or wuk.dtype != q.dtype:
         raise KernelError("latent_query: sizes do not fit")
     qa = torch.empty((T, heads, kv_rank + rot_dim), dtype=torch.float32, device=q.device)
-    check(fn("latent", "sx_latent_query")(ptr(q), ptr(wuk), c_int(heads), c_int(dim), c_int(rot_dim), c_int(kv_rank),
+    check(fn("latent", "sx_latent_query")(ptr(q), c_int(q.shape[1]), ptr(wuk), c_int(heads), c_int(dim), c_int(rot_dim), c_int(kv_rank),
                                           ptr(inv_freq), c_int(rot_dims if inv_freq is not None else 0),
-                                          c_int(1 if pairs else 0), ptr(ctx.positions), ptr(qa), c_int(T),
+                                          c_int(1 if pairs else 0), c_float(magnitude), ptr(ctx.positions), ptr(qa), c_int(T),
                                           c_int(dt_code(q.dtype)), stream()), "latent_query")
     return qa
 
@@ -150,14 +154,22 @@ def latent_expand(kv: torch.Tensor, kr: torch.Tensor, ctx, table: torch.Tensor, 
 
 
 def latent_rotate_q(q: torch.Tensor, heads: int, dim: int, rot_dim: int, inv_freq: Optional[torch.Tensor], rot_dims: int,
-                    pairs: bool, ctx) -> None:
-    """The rotated part of every query head of ``q [T, heads * (dim + rot_dim)]`` rotated in place."""
+                    pairs: bool, ctx, magnitude: float = 1.0) -> torch.Tensor:
+    """The queries ``[T, heads * (dim + rot_dim)]`` with every head's rotated part rotated: in place when ``q`` has exactly
+    those columns, else (``q`` a wider stacked projection that begins with them) into a new tensor."""
     require_cuda(q, inv_freq)
-    if inv_freq is None or rot_dims == 0:
-        return
-    check(fn("latent", "sx_latent_rotate_q")(ptr(q), ptr(ctx.positions), ptr(inv_freq), c_int(rot_dims), c_int(1 if pairs else 0),
+    n = heads * (dim + rot_dim)
+    if q.shape[1] < n:
+        raise KernelError("latent_rotate_q: the queries do not fit")
+    no_rotation = inv_freq is None or rot_dims == 0
+    if q.shape[1] == n and no_rotation:
+        return q
+    out = q if q.shape[1] == n else torch.empty((q.shape[0], n), dtype=q.dtype, device=q.device)
+    check(fn("latent", "sx_latent_rotate_q")(ptr(q), c_int(q.shape[1]), ptr(out), ptr(ctx.positions), ptr(inv_freq),
+                                             c_int(0 if no_rotation else rot_dims), c_int(1 if pairs else 0), c_float(magnitude),
                                              c_int(heads), c_int(dim), c_int(rot_dim), c_int(q.shape[0]), c_int(dt_code(q.dtype)),
                                              stream()), "latent_rotate_q")
+    return out
 
 
 def head_gate(y: torch.Tensor, proj: torch.Tensor, col: int, heads: int, vdim: int) -> None:

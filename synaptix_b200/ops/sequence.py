@@ -119,13 +119,14 @@ def retention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off: Opt
     return out
 
 
-def capped_glu(gu: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
-    """``g sigmoid(alpha g) (u + 1)`` with ``g = min(gu[:, :I], limit)``, ``u = clamp(gu[:, I:], -limit, limit)``."""
+def capped_glu(gu: torch.Tensor, alpha: float, limit: float, form: int = 0) -> torch.Tensor:
+    """``g sigmoid(alpha g) (u + 1)`` with ``g = min(gu[:, :I], limit)``, ``u = clamp(gu[:, I:], -limit, limit)``; with
+    ``form = 1``: ``gelu_tanh(gu[:, :I]) * gu[:, I:]`` (the tanh form of GELU)."""
     require_cuda(gu)
     T, I2 = gu.shape
     out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)
     check(fn("sequence", "sx_capped_glu")(ptr(gu), ptr(out), c_int(T), c_int(I2 // 2), c_float(alpha), c_float(limit),
-                                          c_int(dt_code(gu.dtype)), stream()), "capped_glu")
+                                          c_int(form), c_int(dt_code(gu.dtype)), stream()), "capped_glu")
     return out
 
 

@@ -146,7 +146,32 @@ class PendingLinear:
 
 def plain(t):
     """``t`` as a tensor, whatever deferred form it came in."""
-    return t.materialize() if isinstance(t, (PendingLinear, PendingNorm, ScaledRows, ScaledSum, NormedDelta)) else t
+    return t.materialize() if isinstance(t, (PendingLinear, PendingNorm, ScaledRows, ScaledSum, NormedDelta, NormedSum)) else t
+
+
+class NormedSum:
+    """Mixers side by side, each output behind an RMS norm of its own: ``factor * sum_i rms_norm(x_i) * gain_i`` with
+    ``terms`` one or two ``(x_i [T, width], gain_i float32 [width])``.  A mixer hands this on instead of the sum, so that
+    a block which norms the branch again and adds it into the stream does all of it in one kernel (``NormedDelta`` with
+    this as its ``x``); ``materialize()`` gives the sum as one float32 tensor."""
+    __slots__ = ("terms", "factor", "eps", "_sum")
+
+    def __init__(self, terms, factor: float, eps: float):
+        self.terms = [(x, g) for x, g in terms]
+        if not 1 <= len(self.terms) <= 2:
+            raise ValueError("a normed sum has one or two terms")
+        self.factor, self.eps = float(factor), float(eps)
+        self._sum = None
+
+    @property
+    def shape(self):
+        return self.terms[0][0].shape
+
+    def materialize(self) -> torch.Tensor:
+        if self._sum is None:
+            from .. import ops
+            self._sum = ops.add_normed(None, self.terms, None, self.eps, torch.float32, factor=self.factor)
+        return self._sum
 
 
 class NormedDelta:
@@ -155,20 +180,39 @@ class NormedDelta:
     ``bias`` vectors (a layer norm) and ``bias`` an optional float32 vector over the width (the bias of the branch's
     last product).  A block whose sublayers are normed on both sides hands this on, and a norm that says
     ``takes_normed_delta`` forms branch norm, sum and its own norm in one kernel.  ``materialize()`` gives
-    ``mult * norm(x + bias)`` as one float32 tensor."""
+    ``mult * norm(x + bias)`` as one float32 tensor.
+
+    ``norm`` may also be an RMS norm (it has no ``bias`` vector; ``mult`` is then 1 and there is no product bias), and
+    ``x`` may then be a ``NormedSum``."""
     __slots__ = ("x", "norm", "mult", "bias", "_sum")
 
     def __init__(self, x, norm, mult: float = 1.0, bias=None):
         self.x, self.norm, self.mult, self.bias = x, norm, float(mult), bias
         self._sum = None
+        if not hasattr(norm, "bias") and (self.mult != 1.0 or bias is not None):
+            raise ValueError("a branch behind an RMS norm has neither a factor nor a product bias")
 
     @property
     def shape(self):
         return self.x.shape
 
+    @property
+    def is_rms(self) -> bool:
+        return not hasattr(self.norm, "bias")
+
+    def rms_terms(self):
+        """``(terms, factor)`` as ``ops.add_normed`` takes them."""
+        if isinstance(self.x, NormedSum):
+            return self.x.terms, self.x.factor
+        return [(plain(self.x), None)], 1.0
+
     def materialize(self) -> torch.Tensor:
         if self._sum is None:
             from .. import ops
+            if self.is_rms:
+                terms, factor = self.rms_terms()
+                self._sum = ops.add_normed(None, terms, self.norm.weight, self.norm.eps, torch.float32, factor=factor)
+                return self._sum
             zero = torch.zeros(self.x.shape, dtype=torch.float32, device=self.x.device)
             _, self._sum = ops.add_layernorm(zero, self.x, self.norm.weight, self.norm.bias, self.norm.eps, torch.float32,
                                              post=(self.norm.weight, self.norm.bias), mult=self.mult, delta_bias=self.bias)

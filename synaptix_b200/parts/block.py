@@ -19,6 +19,9 @@ row's root mean square, so one kernel makes both; the sum is handed on as a
 
 ``SandwichBlock``: every sublayer between two norms, ``h += mult * post(sublayer(pre(h)))``,
 with an optional ``TokenShift`` of what the mixer reads.
+
+``PostNormBlock``: a norm on every sublayer's OUTPUT only: ``h += norm1(mixer(h))``, then ``h += norm2(ffn(h))``; the
+sublayers read the stream itself.
 """
 from __future__ import annotations
 
@@ -29,7 +32,7 @@ import torch
 from .. import ops
 from ..cache.store import BundleRequest, StateRequest
 from ..weights.loader import TensorSpec
-from .base import (FeedForward, Mixer, Norm, NormedDelta, Part, PendingLinear, PendingNorm, Runtime, ScaledRows, ScaledSum,
+from .base import (FeedForward, Mixer, Norm, NormedDelta, NormedSum, Part, PendingLinear, PendingNorm, Runtime, ScaledRows, ScaledSum,
                    StepContext, plain, to_device_f32)
 
 
@@ -264,3 +267,54 @@ class SandwichBlock(Part):
             return h, a
         y = self.pre2.add_forward(h, a)
         return h, NormedDelta(self.ffn.forward(y, ctx), self.post2, self.mult)
+
+
+class PostNormBlock(Part):
+    """``h += norm1(mixer(h))``, then ``h += norm2(ffn(h))``: the sublayers read the stream itself (rounded to the compute
+    dtype), and only what they return is normed (RMS norms).  ``norm2`` and ``ffn`` may both be ``None``.
+
+    A branch travels on as a ``NormedDelta`` (whose ``x`` may be a mixer's ``NormedSum``), so that the branch's norm, the
+    sum into the 32-bit stream and the rows the next sublayer reads are one kernel (``ops.add_normed``); the final norm
+    takes the last branch the same way."""
+    takes_pending_product = False
+
+    def __init__(self, mixer: Mixer, norm1: Norm, ffn: Optional[FeedForward] = None, norm2: Optional[Norm] = None):
+        if (norm2 is None) != (ffn is None):
+            raise ValueError("norm2 and ffn come together or not at all")
+        for n in (norm1, norm2):
+            if n is not None and hasattr(n, "bias"):
+                raise ValueError("the norms of a post-norm block are RMS norms")
+        self.mixer, self.norm1, self.ffn, self.norm2 = mixer, norm1, ffn, norm2
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.mixer, self.norm1, self.ffn, self.norm2) if p is not None]
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    @staticmethod
+    def _read(h: torch.Tensor, pending, dtype) -> torch.Tensor:
+        """``h += pending`` and the rows a sublayer reads: the stream in the compute dtype (the stream itself in 32-bit)."""
+        want = None if dtype == torch.float32 else dtype
+        if isinstance(pending, NormedDelta) and pending.is_rms:
+            terms, factor = pending.rms_terms()
+            x = ops.add_normed(h, terms, pending.norm.weight, pending.norm.eps, want, factor=factor)
+        else:
+            pending = plain(pending)
+            if pending is None and want is None:
+                return h
+            x = ops.add_normed(h, [] if pending is None else [(pending, None)], None, 0.0, want)
+        return h if want is None else x
+
+    def forward(self, h: torch.Tensor, pending, ctx: StepContext, cache_view, write_cache: bool = True):
+        dtype = ctx.runtime.dtype
+        x = self._read(h, pending, dtype)
+        if getattr(self.mixer, "returns_normed_sum", False):
+            a = self.mixer.forward(x, ctx, cache_view, write_cache, normed_sum=True)
+        else:
+            a = self.mixer.forward(x, ctx, cache_view, write_cache)
+        a = NormedDelta(a, self.norm1)
+        if self.ffn is None:
+            return h, a
+        y = self._read(h, a, dtype)
+        return h, NormedDelta(self.ffn.forward(y, ctx), self.norm2)

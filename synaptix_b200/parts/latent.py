@@ -3,7 +3,7 @@
 Per token the layer keeps ``c = rmsnorm(Wdkv x)[:kv_rank] * gain`` and one rotated key part of ``rot_dim`` elements
 that all heads share (the last rows of ``Wdkv``, not normed).  Head ``h`` has the key ``[Wuk_h c | k_rot]`` and the
 value ``Wuv_h c``; its query ``[q_h | q_rot_h]`` comes through a latent of its own,
-``Wuq (rmsnorm(Wdq x) * gain)``.  Scores are ``(q_h . Wuk_h c + q_rot_h . k_rot) * scale`` over the visible keys
+``Wuq (rmsnorm(Wdq x) * gain)``, or, with ``q_rank=None``, straight from the input (``Wq x``, tensor ``q``).  Scores are ``(q_h . Wuk_h c + q_rot_h . k_rot) * scale`` over the visible keys
 (causal, optionally a sliding window of ``window`` positions, the query's own included), ordinary softmax; head
 ``h``'s result is multiplied by ``sigmoid(Wg x)_h`` and the heads go through ``Wo``.
 
@@ -39,10 +39,11 @@ class LatentAttention(Mixer):
     accepts_lazy_input = False
     can_defer_output = False
 
-    NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
+    NAMES = {"q": "q", "dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
              "g": "g", "o": "o"}
 
-    def __init__(self, prefix: str, width: int, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int, *,
+    def __init__(self, prefix: str, width: int, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: Optional[int],
+                 kv_rank: int, *,
                  scale: float, position: PositionEncoding, norm_eps: float, window: Optional[int] = None,
                  keep_window="own", own_kv: bool = True, gated: bool = True,
                  names: Optional[Mapping[str, str]] = None):
@@ -50,7 +51,7 @@ class LatentAttention(Mixer):
         it, ``None`` for all); ``"own"``: this layer's ``window``."""
         self.prefix, self.width = prefix, width
         self.heads, self.dim, self.rot_dim, self.vdim = heads, dim, rot_dim, vdim
-        self.q_rank, self.kv_rank = q_rank, kv_rank
+        self.q_rank, self.kv_rank = (q_rank or 0), kv_rank
         self.scale = float(scale)
         self.position = position
         self.norm_eps = float(norm_eps)
@@ -59,34 +60,37 @@ class LatentAttention(Mixer):
         self.own_kv, self.gated = bool(own_kv), bool(gated)
         self.names = n = dict(self.NAMES, **(names or {}))
         p = prefix
-        parts = [(p + n["dq"], q_rank)]
+        # the first columns of the stacked projection: the query latent, or the queries themselves
+        parts = [(p + n["dq"], q_rank)] if self.q_rank else [(p + n["q"], heads * (dim + rot_dim))]
         self.col_dkv = self.col_g = -1
         if own_kv:
-            self.col_dkv = q_rank
+            self.col_dkv = parts[0][1]
             parts.append((p + n["dkv"], kv_rank + rot_dim))
         if gated:
             self.col_g = sum(o for _, o in parts)
             parts.append((p + n["g"], heads))
         self.proj = Linear([x for x, _ in parts], width, [o for _, o in parts])
-        self.uq = Linear(p + n["uq"], q_rank, heads * (dim + rot_dim))
+        self.uq = Linear(p + n["uq"], q_rank, heads * (dim + rot_dim)) if self.q_rank else None
         self.o = Linear(p + n["o"], heads * vdim, width)
         self.dq_gain = self.dkv_gain = self.uk = self.uv = None
 
     def children(self) -> List[Part]:
-        return [self.proj, self.uq, self.o, self.position]
+        return [x for x in (self.proj, self.uq, self.o, self.position) if x is not None]
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         p, n = self.prefix, self.names
-        specs = {p + n["dq_norm"]: TensorSpec((self.q_rank,), "gain"),
-                 p + n["uk"]: TensorSpec((self.heads * self.dim, self.kv_rank), "matrix"),
+        specs = {p + n["uk"]: TensorSpec((self.heads * self.dim, self.kv_rank), "matrix"),
                  p + n["uv"]: TensorSpec((self.heads * self.vdim, self.kv_rank), "matrix")}
+        if self.q_rank:
+            specs[p + n["dq_norm"]] = TensorSpec((self.q_rank,), "gain")
         if self.own_kv:
             specs[p + n["dkv_norm"]] = TensorSpec((self.kv_rank,), "gain")
         return specs
 
     def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         p, n = self.prefix, self.names
-        self.dq_gain = to_device_f32(tensors[p + n["dq_norm"]], rt)
+        if self.q_rank:
+            self.dq_gain = to_device_f32(tensors[p + n["dq_norm"]], rt)
         if self.own_kv:
             self.dkv_gain = to_device_f32(tensors[p + n["dkv_norm"]], rt)
         self.uk = to_device_matrix(tensors[p + n["uk"]], rt)          # [heads * dim, kv_rank]
@@ -121,7 +125,7 @@ class LatentAttention(Mixer):
             made = ctx.scratch["latent_step_pages"] = (torch.from_numpy(table).to(device, non_blocking=True), nxt)
         return made
 
-    def _forward_per_head(self, x, p, q, ctx: StepContext, cache_view: KVView, bt, inv_freq, rot_dims, pairs):
+    def _forward_per_head(self, x, p, q, ctx: StepContext, cache_view: KVView, bt, inv_freq, rot_dims, pairs, mag):
         H, D, Dr, Dv = self.heads, self.dim, self.rot_dim, self.vdim
         c, kr = ops.latent_gather(cache_view.k, ctx, bt, self.kv_rank, Dr)
         kv = ops.linear(c, self.ukv)
@@ -130,7 +134,7 @@ class LatentAttention(Mixer):
         kp = torch.zeros((n_pages, H, 64, D + Dr), dtype=x.dtype, device=x.device)
         vp = torch.zeros((n_pages, H, 64, Dv), dtype=x.dtype, device=x.device)
         ops.latent_expand(kv, kr, ctx, table, H, D, Dr, Dv, kp, vp)
-        ops.latent_rotate_q(q, H, D, Dr, inv_freq, rot_dims, pairs, ctx)
+        q = ops.latent_rotate_q(q, H, D, Dr, inv_freq, rot_dims, pairs, ctx, mag)
         y = ops.attention(q, kp, vp, ctx, table, H, H, D + Dr, self.scale, self.window)
         if self.gated:
             ops.head_gate(y, p, self.col_g, H, Dv)
@@ -147,14 +151,15 @@ class LatentAttention(Mixer):
         rot = self.position.rotation()
         inv_freq, rot_dims = rot if rot is not None else (None, 0)
         pairs = bool(getattr(self.position, "pairs", False))
+        mag = float(getattr(self.position, "magnitude", 1.0))
         bt = ctx.block_tables[cache_view.group]
         p = self.proj.forward(x)
         cq = ops.latent_prepare(p, self.q_rank, self.col_dkv, self.kv_rank, self.rot_dim, self.dq_gain, self.dkv_gain,
-                                self.norm_eps, inv_freq, rot_dims, pairs, ctx, bt, cache_view.k if write_cache else None)
-        q = self.uq.forward(cq)
+                                self.norm_eps, inv_freq, rot_dims, pairs, ctx, bt, cache_view.k if write_cache else None, mag)
+        q = self.uq.forward(cq) if self.q_rank else p          # the queries are the projection's first columns
         if self._whole_prompts(ctx):
-            return self._forward_per_head(x, p, q, ctx, cache_view, bt, inv_freq, rot_dims, pairs)
-        qa = ops.latent_query(q, self.uk, self.heads, self.dim, self.rot_dim, self.kv_rank, inv_freq, rot_dims, pairs, ctx)
+            return self._forward_per_head(x, p, q, ctx, cache_view, bt, inv_freq, rot_dims, pairs, mag)
+        qa = ops.latent_query(q, self.uk, self.heads, self.dim, self.rot_dim, self.kv_rank, inv_freq, rot_dims, pairs, ctx, mag)
         ol = ops.latent_attention(qa, cache_view.k, ctx, bt, self.heads, self.kv_rank, self.rot_dim, self.scale, self.window)
         y = ops.latent_output(ol, self.uv, self.heads, self.vdim, self.kv_rank, p, self.col_g, x.dtype)
         return self.o.forward(y)

@@ -42,8 +42,16 @@ class RMSNorm(Norm):
 
     takes_pending_product = True
     takes_scaled_sum = True
+    takes_normed_delta = True      # of a branch behind an RMS norm (a layer norm's branch is made plain first)
 
     def add_forward(self, h, delta, rows=None, lazy=False):
+        if isinstance(delta, NormedDelta) and delta.is_rms and delta.norm.eps == self.eps:
+            # the branch's norm, the sum into the stream and this norm in one kernel
+            terms, factor = delta.rms_terms()
+            return ops.add_normed(h, terms, delta.norm.weight, self.eps, self._dtype, factor=factor, out_gain=self.weight,
+                                  rows=rows)
+        if isinstance(delta, NormedDelta):
+            delta = delta.materialize()
         if isinstance(delta, ScaledSum):
             # the branches' sum, the sum into the stream and the norm in one kernel
             return ops.add_scaled_rmsnorm(h, delta.terms, [self.weight], self.eps, self._dtype, rows=rows)[0]

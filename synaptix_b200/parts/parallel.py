@@ -5,6 +5,11 @@ The mixers are built ``shared`` (see ``Attention``, ``Retention``): this part st
 into ONE product, lets each mixer write what its output projection reads, times its scale, into its columns of one
 buffer, and runs the output projections as ONE product over the joined inputs.  The cache entry is the bundle of the
 mixers' requests, in their order.
+
+``NormedParallelMixers``: the same arrangement where every mixer's output goes through an RMS norm of its own over the
+model width before the sum: ``factor * sum_i rms_norm(mixer_i(x)) * gain_i``.  The input projections are still ONE
+product; the output projections cannot be joined (each result is normed alone), and the norms and the sum are handed on
+as a ``NormedSum`` to a block that can fold them into its own kernel.
 """
 from __future__ import annotations
 
@@ -13,7 +18,8 @@ from typing import List, Sequence
 import torch
 
 from ..cache.store import BundleRequest
-from .base import Mixer, Part, StepContext
+from ..weights.loader import TensorSpec
+from .base import Mixer, NormedSum, Part, Runtime, StepContext, to_device_f32
 from .linear import JoinedLinear, Linear
 
 
@@ -50,3 +56,50 @@ class ParallelMixers(Mixer):
         for m, col, view, oc, sc in zip(self.mixers, self.cols, views, self.out_cols, self.scales):
             m.mix(a, col, ctx, view, write_cache, out=y, out_col=oc, out_scale=sc)
         return self.o.deferred(y) if defer_output else self.o.forward(y)
+
+
+class NormedParallelMixers(Mixer):
+    """``factor * sum_i rms_norm(mixer_i(x)) * gain_i`` with ``gain_names`` the tensors of the gains (over the model width).
+    The mixers are built ``shared``; one that sets ``needs_input`` is also handed the input ``x`` (for a product that
+    is its own, such as gates that leave 32-bit results)."""
+    accepts_lazy_input = False
+    can_defer_output = False
+    returns_normed_sum = True      # forward(..., normed_sum=True) may return a NormedSum instead of the tensor
+
+    def __init__(self, width: int, mixers: Sequence[Mixer], gain_names: Sequence[str], *, eps: float, factor: float):
+        if len(mixers) != len(gain_names) or not 1 <= len(mixers) <= 2:
+            raise ValueError("one or two mixers, a gain each")
+        self.width = width
+        self.mixers = list(mixers)
+        self.gain_names = list(gain_names)
+        self.eps, self.factor = float(eps), float(factor)
+        names, outs, self.cols = [], [], []
+        for m in self.mixers:
+            self.cols.append(sum(outs))
+            for n, o in m.input_parts():
+                names.append(n)
+                outs.append(o)
+        self.proj = Linear(names, width, outs)
+        self.outs = [Linear(m.output_part()[0], m.output_part()[1], width) for m in self.mixers]
+        self.gains: List[torch.Tensor] = []
+
+    def children(self) -> List[Part]:
+        return [self.proj] + self.outs + self.mixers
+
+    def tensor_specs(self):
+        return {n: TensorSpec((self.width,), "gain") for n in self.gain_names}
+
+    def bind(self, tensors, rt: Runtime) -> None:
+        self.gains = [to_device_f32(tensors[n], rt) for n in self.gain_names]
+
+    def cache_request(self):
+        return BundleRequest(tuple(m.cache_request() for m in self.mixers))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, views, write_cache: bool = True, normed_sum: bool = False):
+        a = self.proj.forward(x)
+        ys = []
+        for m, col, view, o in zip(self.mixers, self.cols, views, self.outs):
+            kw = {"x": x} if getattr(m, "needs_input", False) else {}
+            ys.append(o.forward(m.mix(a, col, ctx, view, write_cache, **kw)))
+        s = NormedSum(list(zip(ys, self.gains)), self.factor, self.eps)
+        return s if normed_sum else s.materialize()

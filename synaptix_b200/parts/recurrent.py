@@ -142,24 +142,40 @@ class MLSTM(Mixer):
     DENOMINATOR_EPS = 1e-6          # added to the denominator max(|n . q|, exp(-m))
 
     def __init__(self, prefix: str, width: int, heads: int, dim: int, vdim: int, *, gate_cap: float,
-                 unit_norm_eps: float, q_scale: Optional[float] = None, names: Optional[Mapping[str, str]] = None):
+                 unit_norm_eps: float, q_scale: Optional[float] = None, names: Optional[Mapping[str, str]] = None,
+                 shared: bool = False):
+        """``shared``: an owner stacks ``input_parts()`` with other mixers' projections and calls ``mix(proj, col, ..., x=x)``
+        (the gates' product stays this part's own: it reads the input ``x`` and leaves 32-bit results)."""
         self.prefix, self.width = prefix, width
+        self.shared = bool(shared)
         self.heads, self.dim, self.vdim = heads, dim, vdim
         self.gate_cap = float(gate_cap)
         self.unit_norm_eps = float(unit_norm_eps)
         self.q_scale = float(q_scale) if q_scale is not None else float(dim) ** -0.5
         self.names = n = dict(self.NAMES, **(names or {}))
         p = prefix
-        self.proj = Linear([p + n["q"], p + n["k"], p + n["v"], p + n["g"]], width,
-                           [heads * dim, heads * dim, heads * vdim, heads * vdim])
+        self.proj = self.o = None
+        if not shared:
+            names_in, outs = zip(*self.input_parts())
+            self.proj = Linear(list(names_in), width, list(outs))
+            self.o = Linear(self.output_part()[0], self.output_part()[1], width)
         # the gates' pre-activations leave their product in 32-bit: they are summed over the whole sequence
         self.gates = Linear([p + n["i"], p + n["f"]], width, [heads, heads])
-        self.o = Linear(p + n["o"], heads * vdim, width)
         self.bias: Optional[torch.Tensor] = None
         self.norm_gain: Optional[torch.Tensor] = None
 
+    needs_input = True              # mix() wants the mixer's input beside the stacked projection
+
+    def input_parts(self):
+        p, n = self.prefix, self.names
+        return [(p + n["q"], self.heads * self.dim), (p + n["k"], self.heads * self.dim), (p + n["v"], self.heads * self.vdim),
+                (p + n["g"], self.heads * self.vdim)]
+
+    def output_part(self):
+        return self.prefix + self.names["o"], self.heads * self.vdim
+
     def children(self) -> List[Part]:
-        return [self.proj, self.gates, self.o]
+        return [self.gates] if self.shared else [self.proj, self.gates, self.o]
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         p, n = self.prefix, self.names
@@ -176,10 +192,14 @@ class MLSTM(Mixer):
                               StateRequest((self.heads, self.dim), torch.float32),
                               StateRequest((self.heads,), torch.float32)))
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, state, write_cache: bool = True):
-        a = self.proj.forward(x)
+    def mix(self, proj: torch.Tensor, col: int, ctx: StepContext, state, write_cache: bool = True, *, x=None, **_):
+        """From a projection whose columns from ``col`` on are this part's q, k, v and output gate, and the mixer's input
+        ``x`` (for the gates): what the output projection reads, ``[T, heads * vdim]``."""
         g = self.gates.forward(x, out_dtype=torch.float32)
         hq, hv = self.heads * self.dim, self.heads * self.vdim
-        y = ops.mlstm(a, 0, hq, 2 * hq, 2 * hq + hv, g, self.bias, self.gate_cap, self.q_scale, self.heads, self.dim,
-                      self.vdim, self.norm_gain, self.unit_norm_eps, self.DENOMINATOR_EPS, state[0], state[1], state[2], ctx)
-        return self.o.forward(y)
+        return ops.mlstm(proj, col, col + hq, col + 2 * hq, col + 2 * hq + hv, g, self.bias, self.gate_cap, self.q_scale,
+                         self.heads, self.dim, self.vdim, self.norm_gain, self.unit_norm_eps, self.DENOMINATOR_EPS,
+                         state[0], state[1], state[2], ctx)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, state, write_cache: bool = True):
+        return self.o.forward(self.mix(self.proj.forward(x), 0, ctx, state, write_cache, x=x))

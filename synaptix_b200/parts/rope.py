@@ -35,9 +35,14 @@ _INV_FREQ = {}
 
 
 class RotaryHalf(PositionEncoding):
+    """``scaling`` (a ``FrequencyRamp``): the slow frequencies are stretched and cos and sin both multiplied by
+    ``magnitude``; the frequencies are then formed in 64-bit and rounded once.  A kernel that rotates for a part with such
+    an encoding multiplies by ``magnitude`` (the parts that take one say so)."""
     pairs = False
 
-    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, scaling: "FrequencyRamp" = None):
+        self.scaling = scaling
+        self.magnitude = 1.0 if scaling is None else scaling.magnitude()
         self.head_dim = head_dim
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
         if self.rotary_dim % 2 or self.rotary_dim > head_dim:
@@ -46,9 +51,15 @@ class RotaryHalf(PositionEncoding):
         self.inv_freq = None
 
     def bind(self, tensors, rt: Runtime) -> None:
-        key = (self.theta, self.rotary_dim, str(rt.device))
+        key = (self.theta, self.rotary_dim, self.scaling, str(rt.device))
         if key not in _INV_FREQ:
-            _INV_FREQ[key] = torch.from_numpy(rotary_inv_freq(self.theta, self.rotary_dim)).to(rt.device)
+            if self.scaling is None:
+                f = rotary_inv_freq(self.theta, self.rotary_dim)
+            else:
+                i = np.arange(self.rotary_dim // 2, dtype=np.float64)
+                f = np.power(np.float64(self.theta), -2.0 * i / self.rotary_dim)
+                f = self.scaling.apply(f, self.theta, self.rotary_dim).astype(np.float32)
+            _INV_FREQ[key] = torch.from_numpy(f).to(rt.device)
         self.inv_freq = _INV_FREQ[key]
 
     def rotation(self):
@@ -62,9 +73,7 @@ class RotaryPairs(RotaryHalf):
     pairs = True
 
     def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, scaling: "FrequencyRamp" = None):
-        super().__init__(head_dim, theta, rotary_dim)
-        self.scaling = scaling
-        self.magnitude = 1.0 if scaling is None else scaling.magnitude()
+        super().__init__(head_dim, theta, rotary_dim, scaling)
 
     def bind(self, tensors, rt: Runtime) -> None:
         # frequencies to the nearest 32-bit value (formed in 64-bit, rounded once)
