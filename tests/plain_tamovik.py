@@ -18,11 +18,20 @@ Notation: ``x [T, W]`` the stream of ONE sequence, ``t`` a position (from 0), ``
     experts       s = sigmoid(Wr x); choice = s + b; groups keep the best by the sum of their two largest choices;
                   top-k of the choices inside kept groups; y = sum_e s_e expert_e(x)
 """
+import json
 import math
+import os
 
 import torch
 
 F = torch.float64
+
+
+def load_folder(path):
+    from safetensors.torch import load_file
+    with open(os.path.join(path, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, {k: v.to(F) for k, v in load_file(os.path.join(path, "model.safetensors")).items()}
 
 
 def rms_norm(x, gain, eps):
@@ -70,20 +79,17 @@ def stretched_frequencies(rot):
 
 
 def rotate_half(v, pos, rot):
-    """``v [..., n]`` at position ``pos``: the first ``rot.dims`` elements rotated, element i with i + dims/2."""
+    """``v [..., n]`` at position ``pos`` (a number, or one position per row of ``v [T, n]``): the first ``rot.dims``
+    elements rotated, element i with i + dims/2."""
     if not rot:
         return v
     dims = rot["dims"]
     f, mag = stretched_frequencies(rot)
     half = dims // 2
-    out = v.clone()
-    for i in range(half):
-        a = pos * f[i]
-        c, s = math.cos(a) * mag, math.sin(a) * mag
-        u, w = v[..., i], v[..., i + half]
-        out[..., i] = u * c - w * s
-        out[..., i + half] = w * c + u * s
-    return out
+    a = torch.as_tensor(pos, dtype=F)[..., None] * torch.tensor(f, dtype=F)          # [..., half]
+    c, s = torch.cos(a) * mag, torch.sin(a) * mag
+    u, w = v[..., :half], v[..., half:dims]
+    return torch.cat([u * c - w * s, w * c + u * s, v[..., dims:]], dim=-1)
 
 
 def latent_attention(x, w, p, m, eps):
@@ -94,13 +100,13 @@ def latent_attention(x, w, p, m, eps):
     q = x @ w[p + "q"].to(F).T                                  # [T, H (D + R)]
     d = x @ w[p + "dkv"].to(F).T                                # [T, rank + R]
     c = rms_norm(d[:, :rank], w[p + "dkv.norm"], eps)
-    kr = torch.stack([rotate_half(d[t, rank:], t, rot) for t in range(T)])
+    kr = rotate_half(d[:, rank:], torch.arange(T), rot)
     uk, uv = w[p + "uk"].to(F), w[p + "uv"].to(F)
     heads = []
     for h in range(H):
         qh = q[:, h * (D + R):(h + 1) * (D + R)]
         qu = qh[:, :D]
-        qr = torch.stack([rotate_half(qh[t, D:], t, rot) for t in range(T)])
+        qr = rotate_half(qh[:, D:], torch.arange(T), rot)
         ku = c @ uk[h * D:(h + 1) * D].T                        # [T, D]
         vh = c @ uv[h * V:(h + 1) * V].T                        # [T, V]
         s = (qu @ ku.T + qr @ kr.T) * m["scale"]
@@ -219,22 +225,25 @@ def experts_ff(x, w, p, spec):
     return out
 
 
-def forward(cfg, w, tokens, layers_out=None):
-    """Logits float64 ``[T, vocab]`` of one sequence; ``layers_out`` (a list) takes the stream after every layer."""
+def forward(cfg, w, tokens, layers_out=None, read=None):
+    """Logits float64 ``[T, vocab]`` of one sequence; ``layers_out`` (a list) takes the stream after every layer.
+    ``read``: a function applied to the stream where a sublayer reads it (say, a rounding to 16 bits: how far the result
+    moves under it tells how well-conditioned an input is)."""
     eps = cfg["norm"]["eps"]
+    read = read or (lambda v: v)
     x = embed(list(tokens), w["embed"], w["bigram"], cfg["embedding"]["bigram"])
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         if layer["type"] == "latent_attention":
-            a = latent_attention(x, w, p + "mix.", layer["mixer"], eps)
+            a = latent_attention(read(x), w, p + "mix.", layer["mixer"], eps)
         elif layer["type"] == "parallel":
-            a = parallel_mixer(x, w, p + "mix.", layer["mixer"], eps)
+            a = parallel_mixer(read(x), w, p + "mix.", layer["mixer"], eps)
         else:
             raise ValueError(layer["type"])
         x = x + rms_norm(a, w[p + "norm1"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            b = dense_ff(x, w, p + "mlp.") if mlp["kind"] == "dense" else experts_ff(x, w, p + "mlp.", mlp)
+            b = dense_ff(read(x), w, p + "mlp.") if mlp["kind"] == "dense" else experts_ff(read(x), w, p + "mlp.", mlp)
             x = x + rms_norm(b, w[p + "norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
