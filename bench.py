@@ -276,9 +276,28 @@ def ledudra_config(width, ff, nh, nkv, hd, rh, runs, vocab):
                 layers=[(soft if i % 2 == 0 else sigm) for i in range(runs)])
 
 
+def tamovik_config(width, ff, nh, nkv, hd, rh, runs, vocab):
+    """``runs`` layers (latent attention, parallel, latent attention) repeated.  Latent attention: heads of ``hd/2``
+    unrotated and ``hd/2`` rotated elements (rotate-half, stretched frequencies) with values of ``hd``, a latent of
+    ``width/8``, every earlier key visible.  Parallel: attention with grouped heads of ``hd``, 3 taps on q and k, chunks of
+    1,000, beside ``rh`` memory heads of ``hd x hd``.  The first layer's feed-forward is dense (``ff``), the others have 16
+    experts of ``ff/4`` in 4 groups of which 2 are kept, 4 a token (as many active weights as the dense one)."""
+    lat = dict(heads=nh, dim=hd // 2, rot_dim=hd // 2, vdim=hd, kv_rank=width // 8, scale=hd ** -0.5,
+               rot=dict(dims=hd // 2, base=5.0e5, scaling=dict(factor=2.0, original=2048, fast=32.0, slow=1.0)))
+    par = dict(left=dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, conv=3, scale=hd ** -0.5, mask=dict(size=1000)),
+               right=dict(heads=rh, dim=hd, vdim=hd, gate_cap=15.0))
+    moe = dict(kind="moe", expert=dict(ff=ff // 4, limit=7.0), router=dict(experts=16, top=4, groups=dict(count=4, keep=2)))
+    layers = []
+    for i in range(runs):
+        mlp = dict(kind="dense", ff=ff) if i == 0 else moe
+        layers.append(dict(type="parallel", mixer=par, mlp=mlp) if i % 3 == 1 else dict(type="latent_attention", mixer=lat, mlp=mlp))
+    return dict(architecture="Tamovik", vocab=vocab, width=width, norm=dict(eps=1e-5),
+                embedding=dict(bigram=dict(buckets=vocab - 1, mul_prev=31, mul_cur=17)), layers=layers)
+
+
 def arch_points(torch, a):
     from synaptix_b200.api import LLM
-    from synaptix_b200.config import LedudraConfig, PidutarConfig, Qwen3Config, VemedraConfig
+    from synaptix_b200.config import LedudraConfig, PidutarConfig, Qwen3Config, TamovikConfig, VemedraConfig
     from synaptix_b200.engine import DecodeRow, Entry
     from synaptix_b200.models import model_skeleton
     from synaptix_b200.parts import Runtime
@@ -337,16 +356,21 @@ def arch_points(torch, a):
 
     for name in (a.arch_sizes.split(",") if a.arch_sizes else list(VEMEDRA_SIZES)):
         width, ff, nh, nkv, hd, rh = VEMEDRA_SIZES[name]
-        if a.arch == "pidutar":
+        if a.arch == "tamovik":
+            measure(TamovikConfig.from_dict(tamovik_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"tamovik_{name}")
+        if a.arch in ("pidutar", "tamovik"):
             measure(PidutarConfig.from_dict(pidutar_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"pidutar_{name}")
-        if a.arch == "ledudra":
+        if a.arch == "tamovik":
+            pass
+        elif a.arch == "ledudra":
             measure(LedudraConfig.from_dict(ledudra_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"ledudra_{name}")
         else:
             measure(VemedraConfig.from_dict(vemedra_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"vemedra_{name}")
         measure(Qwen3Config.from_dict(dict(QWEN3_4B, num_hidden_layers=RUNS, hidden_size=width, num_attention_heads=nh,
                                            num_key_value_heads=nkv, head_dim=hd, intermediate_size=ff, vocab_size=VOCAB,
                                            tie_word_embeddings=False)), f"qwen3_{name}")
-    beside = {"pidutar": "Pidutar beside Vemedra and", "vemedra": "Vemedra beside", "ledudra": "Ledudra beside"}[a.arch]
+    beside = {"pidutar": "Pidutar beside Vemedra and", "vemedra": "Vemedra beside", "ledudra": "Ledudra beside",
+              "tamovik": "Tamovik beside Pidutar and"}[a.arch]
     return {"metric": f"prompt step and decode step, {beside} Qwen3 at equal sizes (bf16, random weights)", "impl": "ours",
             "layer_runs": RUNS, "vocab": VOCAB, "context": CONTEXT, "steps": K, "warmup": a.warmup, "sizes": VEMEDRA_SIZES,
             "data": "synthetic", "dtype": "bf16", "points": out}
@@ -373,10 +397,11 @@ def main():
     ap.add_argument("--short", action="store_true",
                     help="decode only 5 x --steps + --warmup tokens instead of at least 255 (small cases for profilers: "
                          "every launch under a profiler costs a good part of a second)")
-    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "vemedra", "pidutar", "ledudra"],
+    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "vemedra", "pidutar", "ledudra", "tamovik"],
                     help="vemedra: the Vemedra decoder beside Qwen3 at equal sizes (prompt step, decode at batch 1 and 8) instead of "
-                         "the default run; pidutar: the Pidutar decoder beside both; ledudra: the Ledudra decoder beside Qwen3")
-    ap.add_argument("--arch-sizes", default="", help="with --arch vemedra, pidutar or ledudra: which of 1k,2.5k,4k (default: all)")
+                         "the default run; pidutar: the Pidutar decoder beside both; ledudra: the Ledudra decoder beside Qwen3; "
+                         "tamovik: the Tamovik decoder beside Pidutar and Qwen3")
+    ap.add_argument("--arch-sizes", default="", help="with --arch vemedra, pidutar, ledudra or tamovik: which of 1k,2.5k,4k (default: all)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -390,7 +415,7 @@ def main():
     a.warmup = max(a.warmup, 3)
 
     import torch
-    if a.arch in ("vemedra", "pidutar", "ledudra"):
+    if a.arch in ("vemedra", "pidutar", "ledudra", "tamovik"):
         a.steps = min(a.steps, 40)
         print(json.dumps(arch_points(torch, a)))
         return 0

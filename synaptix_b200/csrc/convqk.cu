@@ -1,7 +1,8 @@
 // Head preparation of an attention whose queries and keys pass a short causal convolution over time and are normed over
 // the whole projection, and whose values are the convolved keys (sm_100a), float32 and bfloat16.
 //
-//   convqk_prepare  one block a token.  With u the projection's q and k columns (C = Cq + Ck channels) and taps
+//   convqk_prepare  one block a token (256 threads, or up to 1,024 where the tokens are few).  With u the projection's q
+//                   and k columns (C = Cq + Ck channels) and taps
 //                   w [C, n]:  y_t[c] = sum_j w[c, j] u_(t - n + 1 + j)[c], the earlier rows taken from the step's own
 //                   tokens of the same sequence or, before the portion's start, from the sequence's history (its last
 //                   n - 1 projected rows, oldest first; zeros before position 0).
@@ -14,7 +15,7 @@
 #include "common.cuh"
 
 template <typename T>
-__global__ void __launch_bounds__(256) convqk_prepare_kernel(
+__global__ void __launch_bounds__(1024) convqk_prepare_kernel(
     const T* __restrict__ proj, int row, int col_q, int col_k, int Cq, int Ck, int taps, const float* __restrict__ wq,
     const float* __restrict__ wk, const float* __restrict__ gq, const float* __restrict__ gk, float eps, float* __restrict__ hist,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ seq_past,
@@ -24,12 +25,12 @@ __global__ void __launch_bounds__(256) convqk_prepare_kernel(
   __shared__ float red[33];
   pdl_wait();
   pdl_trigger();
-  const int t = blockIdx.x, tid = threadIdx.x;
+  const int t = blockIdx.x, tid = threadIdx.x, NT = blockDim.x;
   const int s = seq_of_token[t], pos = positions[t], past = seq_past[s];
   const int C = Cq + Ck, P = taps - 1;
   float* hs = hist + (size_t)seq_slots[s] * P * C;
   float sq = 0.f, sk = 0.f;
-  for (int c = tid; c < C; c += 256) {
+  for (int c = tid; c < C; c += NT) {
     const bool is_q = c < Cq;
     const int pc = is_q ? col_q + c : col_k + (c - Cq);
     const float* w = is_q ? wq + (size_t)c * taps : wk + (size_t)(c - Cq) * taps;
@@ -52,10 +53,10 @@ __global__ void __launch_bounds__(256) convqk_prepare_kernel(
   sq = block_sum(sq, red);
   sk = block_sum(sk, red);
   const float rq = rsqrtf(sq / (float)Cq + eps), rk = rsqrtf(sk / (float)Ck + eps);
-  for (int c = tid; c < Cq; c += 256) q_out[(size_t)t * Cq + c] = from_f32<T>(ys[c] * rq * gq[c]);
+  for (int c = tid; c < Cq; c += NT) q_out[(size_t)t * Cq + c] = from_f32<T>(ys[c] * rq * gq[c]);
   if (k_pages == nullptr) return;
   const int page = block_table[(size_t)s * maxp + (pos >> 6)];
-  for (int c = tid; c < Ck; c += 256) {
+  for (int c = tid; c < Ck; c += NT) {
     const int g = c / D, d = c - g * D;
     const size_t at = (((size_t)page * G + g) * SX_PAGE + (pos & 63)) * D + d;
     const float y = ys[Cq + c];
@@ -94,13 +95,16 @@ extern "C" int sx_convqk_prepare(const void* proj, int row, int col_q, int col_k
     return SX_ERR_SIZE;
   const size_t smem = (size_t)(Cq + Ck) * sizeof(float);
   if (smem > 48 * 1024) return SX_ERR_SIZE;
+  // few tokens (single-token steps): a thread walks a handful of channels, each a chain of dependent trips to memory
+  const int C = Cq + Ck;
+  const int nt = n_tokens <= 296 ? (C >= 2048 ? 1024 : (C >= 1024 ? 512 : 256)) : 256;
   int rc;
   if (dt == SX_F32)
-    rc = sx_launch(convqk_prepare_kernel<float>, dim3(n_tokens), dim3(256), smem, stream, (const float*)proj, row, col_q, col_k, Cq,
+    rc = sx_launch(convqk_prepare_kernel<float>, dim3(n_tokens), dim3(nt), smem, stream, (const float*)proj, row, col_q, col_k, Cq,
                    Ck, taps, wq, wk, gq, gk, eps, hist, positions, seq_of_token, seq_past, seq_slots, block_table, maxp,
                    (float*)q_out, (float*)k_pages, (float*)v_pages, G, D, all_single);
   else if (dt == SX_BF16)
-    rc = sx_launch(convqk_prepare_kernel<bf16>, dim3(n_tokens), dim3(256), smem, stream, (const bf16*)proj, row, col_q, col_k, Cq,
+    rc = sx_launch(convqk_prepare_kernel<bf16>, dim3(n_tokens), dim3(nt), smem, stream, (const bf16*)proj, row, col_q, col_k, Cq,
                    Ck, taps, wq, wk, gq, gk, eps, hist, positions, seq_of_token, seq_past, seq_slots, block_table, maxp,
                    (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, G, D, all_single);
   else

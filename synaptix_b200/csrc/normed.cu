@@ -1,5 +1,6 @@
 // Branches that are normed on their way into the residual stream (sm_100a), float32 and bfloat16 branches, all sums
-// and norms 32-bit.  One block a row; the row stays in shared memory between its passes.
+// and norms 32-bit.  One block a row (256 threads, or up to 1,024 where the rows are few); the row stays in shared memory
+// between its passes.
 //
 //   add_normed:   v   = a                                        (one term without a gain), or
 //                 v   = f * (rms_norm(a) ga + rms_norm(b) gb)     (one or two terms with gains: mixers side by side)
@@ -17,7 +18,7 @@ __device__ __forceinline__ float ldf(const void* p, int dt, size_t i) {
 }
 
 template <typename TO>
-__global__ void __launch_bounds__(256) add_normed_kernel(
+__global__ void __launch_bounds__(1024) add_normed_kernel(
     float* __restrict__ h, const void* __restrict__ a, int a_dt, const float* __restrict__ ga,
     const void* __restrict__ b, int b_dt, const float* __restrict__ gb, float factor, const float* __restrict__ gp,
     const float* __restrict__ go, float eps, TO* __restrict__ y, const int* __restrict__ rows, int H, int write_h) {
@@ -25,18 +26,18 @@ __global__ void __launch_bounds__(256) add_normed_kernel(
   __shared__ float red[33];
   pdl_wait();
   pdl_trigger();
-  const int r = blockIdx.x, tid = threadIdx.x;
+  const int r = blockIdx.x, tid = threadIdx.x, NT = blockDim.x;
   const int t = rows ? rows[r] : r;
   const size_t base = (size_t)t * H;
   const float inv_h = 1.f / (float)H;
   float ssv = 0.f;
   if (a == nullptr) {
-    for (int i = tid; i < H; i += 256) row[i] = 0.f;
+    for (int i = tid; i < H; i += NT) row[i] = 0.f;
   } else if (ga == nullptr) {
-    for (int i = tid; i < H; i += 256) { const float v = ldf(a, a_dt, base + i); row[i] = v; ssv += v * v; }
+    for (int i = tid; i < H; i += NT) { const float v = ldf(a, a_dt, base + i); row[i] = v; ssv += v * v; }
   } else {
     float sa = 0.f, sb = 0.f;
-    for (int i = tid; i < H; i += 256) {
+    for (int i = tid; i < H; i += NT) {
       const float va = ldf(a, a_dt, base + i);
       sa += va * va;
       if (b) { const float vb = ldf(b, b_dt, base + i); sb += vb * vb; }
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(256) add_normed_kernel(
     const float ra = rsqrtf(sa * inv_h + eps);
     float rb = 0.f;
     if (b) { sb = block_sum(sb, red); rb = rsqrtf(sb * inv_h + eps); }
-    for (int i = tid; i < H; i += 256) {
+    for (int i = tid; i < H; i += NT) {
       float v = ldf(a, a_dt, base + i) * ra * ga[i];
       if (b) v += ldf(b, b_dt, base + i) * rb * gb[i];
       v *= factor;
@@ -56,7 +57,7 @@ __global__ void __launch_bounds__(256) add_normed_kernel(
   float rv = 1.f;
   if (gp) { ssv = block_sum(ssv, red); rv = rsqrtf(ssv * inv_h + eps); }
   float ssq = 0.f;
-  for (int i = tid; i < H; i += 256) {           // a thread passes over the same elements in every loop: no barrier needed
+  for (int i = tid; i < H; i += NT) {           // a thread passes over the same elements in every loop: no barrier needed
     float acc = gp ? row[i] * rv * gp[i] : row[i];
     if (h) {
       acc += h[base + i];
@@ -70,9 +71,9 @@ __global__ void __launch_bounds__(256) add_normed_kernel(
   if (go) {
     ssq = block_sum(ssq, red);
     const float ro = rsqrtf(ssq * inv_h + eps);
-    for (int i = tid; i < H; i += 256) yr[i] = from_f32<TO>(row[i] * ro * go[i]);
+    for (int i = tid; i < H; i += NT) yr[i] = from_f32<TO>(row[i] * ro * go[i]);
   } else {
-    for (int i = tid; i < H; i += 256) yr[i] = from_f32<TO>(row[i]);
+    for (int i = tid; i < H; i += NT) yr[i] = from_f32<TO>(row[i]);
   }
 }
 
@@ -83,14 +84,17 @@ extern "C" int sx_add_normed(float* h, const void* a, int a_dt, const float* ga,
   if (H <= 0 || (b != nullptr && (a == nullptr || ga == nullptr || gb == nullptr))) return SX_ERR_SIZE;
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return SX_ERR_SIZE;
+  // few rows (single-token steps): a thread an element or two, so that each pass is one trip to memory; many rows: 256
+  // threads a row and several rows an SM
+  const int nt = R <= 296 ? (H >= 2048 ? 1024 : (H >= 1024 ? 512 : 256)) : 256;
   if (y == nullptr || y_dt == SX_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(add_normed_kernel<float>, dim3(R), dim3(256), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
+    return sx_launch(add_normed_kernel<float>, dim3(R), dim3(nt), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
                      (float*)y, rows, H, write_h);
   }
   if (y_dt == SX_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(add_normed_kernel<bf16>, dim3(R), dim3(256), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
+    return sx_launch(add_normed_kernel<bf16>, dim3(R), dim3(nt), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
                      (bf16*)y, rows, H, write_h);
   }
   return SX_ERR_DTYPE;

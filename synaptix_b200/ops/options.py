@@ -28,7 +28,8 @@ switches in its runtime options (crates/synaptix-config/src/runtime.rs, ``AttnBa
 ``pdl``             kernels are launched with programmatic dependent launch
 ``branch_streams``  single-token steps of a block whose mixer and feed-forward read the same stream: the feed-forward's
                     kernels run on a second CUDA stream beside the mixer's (inside a captured step: two branches of
-                    the graph), else one after the other
+                    the graph), else one after the other; likewise the second of two mixers that run side by side
+                    behind norms of their own
 """
 from __future__ import annotations
 

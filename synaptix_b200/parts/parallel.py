@@ -17,6 +17,7 @@ from typing import List, Sequence
 
 import torch
 
+from .. import ops
 from ..cache.store import BundleRequest
 from ..weights.loader import TensorSpec
 from .base import Mixer, NormedSum, Part, Runtime, StepContext, to_device_f32
@@ -95,11 +96,32 @@ class NormedParallelMixers(Mixer):
     def cache_request(self):
         return BundleRequest(tuple(m.cache_request() for m in self.mixers))
 
+    def _branch(self, i: int, a, x, ctx, views, write_cache):
+        m = self.mixers[i]
+        kw = {"x": x} if getattr(m, "needs_input", False) else {}
+        return self.outs[i].forward(m.mix(a, self.cols[i], ctx, views[i], write_cache, **kw))
+
     def forward(self, x: torch.Tensor, ctx: StepContext, views, write_cache: bool = True, normed_sum: bool = False):
+        """In single-token steps, where each mixer is a chain of small kernels, the second mixer runs on a second stream
+        beside the first (option ``branch_streams``; inside a captured step: two branches of the graph).  It begins behind
+        the stacked projection (an event) and the step's stream waits for its end before anything reads its result; what
+        crosses the streams lives until this function returns or is read on the step's stream behind that wait, and the
+        second stream does nothing more before the next such event, so nothing is handed out again too early."""
         a = self.proj.forward(x)
-        ys = []
-        for m, col, view, o in zip(self.mixers, self.cols, views, self.outs):
-            kw = {"x": x} if getattr(m, "needs_input", False) else {}
-            ys.append(o.forward(m.mix(a, col, ctx, view, write_cache, **kw)))
+        if len(self.mixers) == 2 and ctx.all_single and ops.OPTIONS.branch_streams and x.is_cuda:
+            from .block import _side_stream
+            main, side = torch.cuda.current_stream(x.device), _side_stream(x.device)
+            fork = torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                y1 = self._branch(1, a, x, ctx, views, write_cache)
+                join = torch.cuda.Event()
+                join.record(side)
+            y0 = self._branch(0, a, x, ctx, views, write_cache)
+            main.wait_event(join)
+            ys = [y0, y1]
+        else:
+            ys = [self._branch(i, a, x, ctx, views, write_cache) for i in range(len(self.mixers))]
         s = NormedSum(list(zip(ys, self.gains)), self.factor, self.eps)
         return s if normed_sum else s.materialize()

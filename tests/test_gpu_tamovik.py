@@ -491,6 +491,36 @@ def test_token_by_token_from_the_first_token(engines, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["TA", "TF"])
+def test_mixers_on_two_streams_change_no_bit(name, dtype):
+    """Single-token steps run a parallel layer's second mixer on a second stream beside the first (captured: two
+    branches of the graph).  The same steps with the mixers one after the other, and a second time on two streams in
+    slots and pages used again, give the same bits."""
+    from synaptix_b200 import ops
+    from synaptix_b200.engine import Engine, Entry
+    from synaptix_b200.models import load_model
+    toks = [tokens(name, n, 60 + n) for n in (90, 37, 64)]
+
+    def run(eng):
+        slots = [eng.open() for _ in toks]
+        out = [eng.step([Entry(s, t[:20], [19]) for s, t in zip(slots, toks)])]
+        for j in range(20, 37):
+            out.append(eng.step([Entry(s, [t[j]], [0]) for s, t in zip(slots, toks)]))
+        for j in range(37, 64):                                  # the shorter requests end earlier
+            out.append(eng.step([Entry(s, [t[j]], [0]) for s, t in zip(slots[::2], toks[::2])]))
+        for s in slots:
+            eng.close(s)
+        return torch.cat(out).cpu()
+    with ops.options(branch_streams=False):
+        eng = Engine(load_model(folder(name), dtype=dtype), max_tokens=1024, max_seqs=3)
+        ref = run(eng)
+    eng = Engine(load_model(folder(name), dtype=dtype), max_tokens=1024, max_seqs=3)
+    first, second = run(eng), run(eng)
+    assert any(c.graph is not None for c in eng._captured.values())
+    assert torch.equal(first, ref) and torch.equal(second, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 @pytest.mark.parametrize("size", [2, 3, 7, 64, 100])
 def test_prompts_in_portions(engines, name, dtype, size):
