@@ -13,11 +13,47 @@
 //                 (its last token), which the same block then moves on to the portion's last token.
 #include "common.cuh"
 
-__device__ __forceinline__ float ldf(const void* p, int dt, size_t i) {
-  return dt == SX_F32 ? ((const float*)p)[i] : __bfloat162float(((const bf16*)p)[i]);
+// W elements from a W-aligned place: W = 1, or W = 4 where the width is a multiple of 4 and every array 16-byte aligned
+template <int W> __device__ __forceinline__ void ldv(const void* p, int dt, size_t i, float (&v)[W]) {
+  if (W == 4) {
+    if (dt == SX_F32) {
+      const float4 f = *reinterpret_cast<const float4*>((const float*)p + i);
+      v[0] = f.x; v[1 % W] = f.y; v[2 % W] = f.z; v[3 % W] = f.w;
+    } else {
+      const uint2 u = *reinterpret_cast<const uint2*>((const bf16*)p + i);
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+      v[0] = __low2float(lo); v[1 % W] = __high2float(lo); v[2 % W] = __low2float(hi); v[3 % W] = __high2float(hi);
+    }
+  } else {
+    v[0] = dt == SX_F32 ? ((const float*)p)[i] : __bfloat162float(((const bf16*)p)[i]);
+  }
+}
+template <int W> __device__ __forceinline__ void ldfv(const float* p, size_t i, float (&v)[W]) {
+  if (W == 4) {
+    const float4 f = *reinterpret_cast<const float4*>(p + i);
+    v[0] = f.x; v[1 % W] = f.y; v[2 % W] = f.z; v[3 % W] = f.w;
+  } else {
+    v[0] = p[i];
+  }
+}
+template <int W> __device__ __forceinline__ void stfv(float* p, size_t i, const float (&v)[W]) {
+  if (W == 4) *reinterpret_cast<float4*>(p + i) = make_float4(v[0], v[1 % W], v[2 % W], v[3 % W]);
+  else p[i] = v[0];
+}
+template <int W> __device__ __forceinline__ void stv(float* p, size_t i, const float (&v)[W]) { stfv<W>(p, i, v); }
+template <int W> __device__ __forceinline__ void stv(bf16* p, size_t i, const float (&v)[W]) {
+  if (W == 4) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1 % W]), hi = __floats2bfloat162_rn(v[2 % W], v[3 % W]);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&lo);
+    u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p + i) = u;
+  } else {
+    p[i] = __float2bfloat16_rn(v[0]);
+  }
 }
 
-template <typename TO>
+template <typename TO, int W>
 __global__ void __launch_bounds__(1024) add_normed_kernel(
     float* __restrict__ h, const void* __restrict__ a, int a_dt, const float* __restrict__ ga,
     const void* __restrict__ b, int b_dt, const float* __restrict__ gb, float factor, const float* __restrict__ gp,
@@ -26,55 +62,107 @@ __global__ void __launch_bounds__(1024) add_normed_kernel(
   __shared__ float red[33];
   pdl_wait();
   pdl_trigger();
-  const int r = blockIdx.x, tid = threadIdx.x, NT = blockDim.x;
+  const int r = blockIdx.x, tid = threadIdx.x * W, NT = blockDim.x * W;
   const int t = rows ? rows[r] : r;
   const size_t base = (size_t)t * H;
   const float inv_h = 1.f / (float)H;
   float ssv = 0.f;
+  float v[W], u[W], g[W];
   if (a == nullptr) {
-    for (int i = tid; i < H; i += NT) row[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) v[j] = 0.f;
+    for (int i = tid; i < H; i += NT) stfv<W>(row, i, v);
   } else if (ga == nullptr) {
-    for (int i = tid; i < H; i += NT) { const float v = ldf(a, a_dt, base + i); row[i] = v; ssv += v * v; }
+    for (int i = tid; i < H; i += NT) {
+      ldv<W>(a, a_dt, base + i, v);
+      stfv<W>(row, i, v);
+#pragma unroll
+      for (int j = 0; j < W; ++j) ssv += v[j] * v[j];
+    }
   } else {
     float sa = 0.f, sb = 0.f;
     for (int i = tid; i < H; i += NT) {
-      const float va = ldf(a, a_dt, base + i);
-      sa += va * va;
-      if (b) { const float vb = ldf(b, b_dt, base + i); sb += vb * vb; }
+      ldv<W>(a, a_dt, base + i, v);
+#pragma unroll
+      for (int j = 0; j < W; ++j) sa += v[j] * v[j];
+      if (b) {
+        ldv<W>(b, b_dt, base + i, u);
+#pragma unroll
+        for (int j = 0; j < W; ++j) sb += u[j] * u[j];
+      }
     }
     sa = block_sum(sa, red);
     const float ra = rsqrtf(sa * inv_h + eps);
     float rb = 0.f;
     if (b) { sb = block_sum(sb, red); rb = rsqrtf(sb * inv_h + eps); }
     for (int i = tid; i < H; i += NT) {
-      float v = ldf(a, a_dt, base + i) * ra * ga[i];
-      if (b) v += ldf(b, b_dt, base + i) * rb * gb[i];
-      v *= factor;
-      row[i] = v;
-      ssv += v * v;
+      ldv<W>(a, a_dt, base + i, v);
+      ldfv<W>(ga, i, g);
+#pragma unroll
+      for (int j = 0; j < W; ++j) v[j] = v[j] * ra * g[j];
+      if (b) {
+        ldv<W>(b, b_dt, base + i, u);
+        ldfv<W>(gb, i, g);
+#pragma unroll
+        for (int j = 0; j < W; ++j) v[j] += u[j] * rb * g[j];
+      }
+#pragma unroll
+      for (int j = 0; j < W; ++j) { v[j] *= factor; ssv += v[j] * v[j]; }
+      stfv<W>(row, i, v);
     }
   }
   float rv = 1.f;
   if (gp) { ssv = block_sum(ssv, red); rv = rsqrtf(ssv * inv_h + eps); }
   float ssq = 0.f;
-  for (int i = tid; i < H; i += NT) {           // a thread passes over the same elements in every loop: no barrier needed
-    float acc = gp ? row[i] * rv * gp[i] : row[i];
-    if (h) {
-      acc += h[base + i];
-      if (write_h) h[base + i] = acc;
+  for (int i = tid; i < H; i += NT) {            // a thread passes over the same elements in every loop: no barrier needed
+    ldfv<W>(row, i, v);
+    if (gp) {
+      ldfv<W>(gp, i, g);
+#pragma unroll
+      for (int j = 0; j < W; ++j) v[j] = v[j] * rv * g[j];
     }
-    row[i] = acc;
-    ssq += acc * acc;
+    if (h) {
+      ldfv<W>(h, base + i, u);
+#pragma unroll
+      for (int j = 0; j < W; ++j) v[j] += u[j];
+      if (write_h) stfv<W>(h, base + i, v);
+    }
+    stfv<W>(row, i, v);
+#pragma unroll
+    for (int j = 0; j < W; ++j) ssq += v[j] * v[j];
   }
   if (y == nullptr) return;
   TO* yr = y + (size_t)r * H;
   if (go) {
     ssq = block_sum(ssq, red);
     const float ro = rsqrtf(ssq * inv_h + eps);
-    for (int i = tid; i < H; i += NT) yr[i] = from_f32<TO>(row[i] * ro * go[i]);
+    for (int i = tid; i < H; i += NT) {
+      ldfv<W>(row, i, v);
+      ldfv<W>(go, i, g);
+#pragma unroll
+      for (int j = 0; j < W; ++j) v[j] = v[j] * ro * g[j];
+      stv<W>(yr, i, v);
+    }
   } else {
-    for (int i = tid; i < H; i += NT) yr[i] = from_f32<TO>(row[i]);
+    for (int i = tid; i < H; i += NT) {
+      ldfv<W>(row, i, v);
+      stv<W>(yr, i, v);
+    }
   }
+}
+
+template <typename TO, int W>
+static int add_normed_launch(float* h, const void* a, int a_dt, const float* ga, const void* b, int b_dt, const float* gb,
+                             float factor, const float* gp, const float* go, float eps, void* y, const int* rows, int R, int H,
+                             int write_h, cudaStream_t stream) {
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<TO, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  // few rows (single-token steps): a thread an element or a handful, so that each pass is one trip to memory; many rows:
+  // 256 threads a row and several rows an SM
+  const int per = (H / W + 31) / 32 * 32;
+  const int nt = R <= 296 ? (per > 1024 ? 1024 : (per < 128 ? 128 : per)) : 256;
+  return sx_launch(add_normed_kernel<TO, W>, dim3(R), dim3(nt), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
+                   (TO*)y, rows, H, write_h);
 }
 
 extern "C" int sx_add_normed(float* h, const void* a, int a_dt, const float* ga, const void* b, int b_dt, const float* gb,
@@ -82,21 +170,14 @@ extern "C" int sx_add_normed(float* h, const void* a, int a_dt, const float* ga,
                              int R, int H, int write_h, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (H <= 0 || (b != nullptr && (a == nullptr || ga == nullptr || gb == nullptr))) return SX_ERR_SIZE;
-  const size_t smem = (size_t)H * sizeof(float);
-  if (smem > 200 * 1024) return SX_ERR_SIZE;
-  // few rows (single-token steps): a thread an element or two, so that each pass is one trip to memory; many rows: 256
-  // threads a row and several rows an SM
-  const int nt = R <= 296 ? (H >= 2048 ? 1024 : (H >= 1024 ? 512 : 256)) : 256;
-  if (y == nullptr || y_dt == SX_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(add_normed_kernel<float>, dim3(R), dim3(nt), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
-                     (float*)y, rows, H, write_h);
-  }
-  if (y_dt == SX_BF16) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(add_normed_kernel<bf16>, dim3(R), dim3(nt), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
-                     (bf16*)y, rows, H, write_h);
-  }
+  if ((size_t)H * sizeof(float) > 200 * 1024) return SX_ERR_SIZE;
+  const uintptr_t all = (uintptr_t)h | (uintptr_t)a | (uintptr_t)ga | (uintptr_t)b | (uintptr_t)gb | (uintptr_t)gp | (uintptr_t)go |
+                        (uintptr_t)y;
+  const bool v4 = (H % 4 == 0) && (all % 16 == 0);
+#define AN_GO(TO, W) return add_normed_launch<TO, W>(h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps, y, rows, R, H, write_h, stream)
+  if (y == nullptr || y_dt == SX_F32) { if (v4) AN_GO(float, 4); AN_GO(float, 1); }
+  if (y_dt == SX_BF16) { if (v4) AN_GO(bf16, 4); AN_GO(bf16, 1); }
+#undef AN_GO
   return SX_ERR_DTYPE;
 }
 

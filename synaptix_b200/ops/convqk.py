@@ -13,18 +13,19 @@ def convqk_prepare(proj: torch.Tensor, col_q: int, col_k: int, heads: int, kv_he
                    taps_k: torch.Tensor, gain_q: torch.Tensor, gain_k: torch.Tensor, eps: float, hist: torch.Tensor, ctx,
                    block_table: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor]) -> torch.Tensor:
     """From ``proj [T, row]`` (q in ``heads * dim`` columns from ``col_q``, k in ``kv_heads * dim`` from ``col_k``):
-    both convolved over each sequence's own positions with ``taps_* [channels, n]`` (float32; ``hist`` float32
+    both convolved over each sequence's own positions with ``taps_*`` (float32, taps-major: ``[n, channels]``, the
+    transpose of the stored ``[channels, n]``; ``hist`` float32
     ``[slots, n - 1, Cq + Ck]`` holds every sequence's last ``n - 1`` projected rows and is moved on); the convolved
     keys are the values; queries and keys are RMS-normed over ALL their channels times ``gain_*``.  Returns the
     queries ``[T, heads * dim]``; keys and values go into the cache pages (``None``: nothing is cached)."""
     require_cuda(proj, taps_q, taps_k, gain_q, gain_k, hist, block_table, k_pages, v_pages)
     T, row = proj.shape
     Cq, Ck = heads * dim, kv_heads * dim
-    taps = taps_q.shape[1]
+    taps = taps_q.shape[0]
     for t in (taps_q, taps_k, gain_q, gain_k, hist):
         if t.dtype != torch.float32:
             raise KernelError("convqk_prepare: taps, gains and the history are float32")
-    if (tuple(taps_q.shape) != (Cq, taps) or tuple(taps_k.shape) != (Ck, taps) or gain_q.numel() != Cq or gain_k.numel() != Ck
+    if (tuple(taps_q.shape) != (taps, Cq) or tuple(taps_k.shape) != (taps, Ck) or gain_q.numel() != Cq or gain_k.numel() != Ck
             or tuple(hist.shape[1:]) != (taps - 1, Cq + Ck)):
         raise KernelError("convqk_prepare: the taps, gains or history do not fit the heads")
     if k_pages is not None and (v_pages is None or k_pages.dtype != proj.dtype or tuple(k_pages.shape[1:]) != (kv_heads, 64, dim)

@@ -85,7 +85,7 @@ def _pick_latent_splits(ctx, heads: int, window: Optional[int], device) -> int:
         _SMS[idx] = torch.cuda.get_device_properties(device).multi_processor_count
     blocks = ctx.n_tokens * ((heads + 7) // 8)
     want = (2 * _SMS[idx] + blocks - 1) // blocks
-    return max(1, min(want, tiles // 2, 32))        # (a window of 1,000 keys never asks for more than 15)
+    return max(1, min(want, tiles // 2, 16))
 
 
 def latent_attention(qa: torch.Tensor, k_pages: torch.Tensor, ctx, block_table: torch.Tensor, heads: int, kv_rank: int,

@@ -79,8 +79,9 @@ class ConvNormAttention(Mixer):
 
     def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         p, n = self.prefix, self.names
-        self.taps_q = to_device_f32(tensors[p + n["q_conv"]], rt)
-        self.taps_k = to_device_f32(tensors[p + n["k_conv"]], rt)
+        # taps-major on the device ([taps, channels]): neighbouring channels' weights of one tap lie together
+        self.taps_q = to_device_f32(tensors[p + n["q_conv"]].t(), rt)
+        self.taps_k = to_device_f32(tensors[p + n["k_conv"]].t(), rt)
         self.gain_q = to_device_f32(tensors[p + n["q_norm"]], rt)
         self.gain_k = to_device_f32(tensors[p + n["k_norm"]], rt)
 

@@ -176,12 +176,13 @@ def run_conv_attention(W, xs, cols, heads, kv_heads, dim, taps, chunk, scale, le
     hist = torch.full((max(slots) + 2, taps - 1, Cq + Ck), float("nan")).cuda()
     hist[slots] = 0.0
     f32 = lambda n: W[n].float().cuda()
+    taps_major = lambda n: W[n].float().t().contiguous().cuda()          # the kernel takes the taps as [taps, channels]
     outs = [[] for _ in lengths]
     for past, new, who in portions(lengths, cuts):
         bt = i32([tables[i] + [0] * (maxp - len(tables[i])) for i in who])
         ctx = step_ctx(past, new, [slots[i] for i in who], [bt], DT[dtype])
         proj = torch.cat([xs[i][p:p + n] for i, p, n in zip(who, past, new)]).cuda()
-        q = ops.convqk_prepare(proj, cols[0], cols[1], heads, kv_heads, dim, f32("p.q.conv"), f32("p.k.conv"), f32("p.q.norm"),
+        q = ops.convqk_prepare(proj, cols[0], cols[1], heads, kv_heads, dim, taps_major("p.q.conv"), taps_major("p.k.conv"), f32("p.q.norm"),
                                f32("p.k.norm"), 1e-5, hist, ctx, bt, kp, vp)
         y = ops.attention(q, kp, vp, ctx, bt, heads, kv_heads, dim, scale, None, chunk=chunk)
         ops.sigmoid_gate(y, proj, cols[2])
