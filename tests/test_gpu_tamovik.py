@@ -14,7 +14,7 @@ from tiny_tamovik import CONFIGS, folder, oracle, oracle_logits, tokens
 
 pytestmark = pytest.mark.gpu
 
-NAMES = ["TA", "TB", "TF"]
+NAMES = ["TA", "TB", "TF", "TG"]
 DTYPES = ["float32", "bfloat16"]
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 F = torch.float64

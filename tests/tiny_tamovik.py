@@ -72,7 +72,16 @@ TF = _cfg(256, 128, 1e-5, 509, 31, 17,
            _par(8, 2, 32, 2, 0.18, None, 2, 32, 32, 15.0, _dense(128))])
 TF_INIT = dict(seed=13, std_matrix=0.08, std_embedding=0.4, std_gain=0.1, std_bias=0.3)
 
-CONFIGS = {"TA": (TA, TA_INIT), "TB": (TB, TB_INIT), "TF": (TF, TF_INIT)}
+# attention WITHOUT chunks at head sizes 128 and 64 (the library's plain attention kernels: tcgen05 for prompts, pages by
+# TMA for single tokens, with values read from pages of their own that hold the unnormed keys), four taps, a latent layer
+# between them whose whole prompts run over per-head keys of 128, experts in groups of four of which one is kept
+TG = _cfg(300, 256, 1e-5, 127, 3, 11,
+          [_par(4, 2, 128, 4, 0.09, None, 2, 64, 64, 12.0, _dense(512)),
+           _lat(2, 64, 64, 128, 64, 0.09, (64, 1.0e5, 2.0, 256, 32.0, 1.0), _moe(128, 1.5, 8, 2, (2, 1))),
+           _par(4, 1, 64, 2, 0.125, None, 1, 128, 128, 15.0, _moe(64, 2.0, 4, 1))])
+TG_INIT = dict(seed=21, std_matrix=0.06, std_embedding=0.4, std_gain=0.1, std_bias=0.3)
+
+CONFIGS = {"TA": (TA, TA_INIT), "TB": (TB, TB_INIT), "TF": (TF, TF_INIT), "TG": (TG, TG_INIT)}
 
 _FOLDERS = {}
 
