@@ -283,7 +283,7 @@ def tamovik_config(width, ff, nh, nkv, hd, rh, runs, vocab):
     1,000, beside ``rh`` memory heads of ``hd x hd``.  The first layer's feed-forward is dense (``ff``), the others have 16
     experts of ``ff/4`` in 4 groups of which 2 are kept, 4 a token (as many active weights as the dense one)."""
     lat = dict(heads=nh, dim=hd // 2, rot_dim=hd // 2, vdim=hd, kv_rank=width // 8, scale=hd ** -0.5,
-               rot=dict(dims=hd // 2, base=5.0e5, scaling=dict(factor=2.0, original=2048, fast=32.0, slow=1.0)))
+               rot=dict(dims=hd // 2, base=1.0e6, scaling=dict(factor=4.0, original=4096, fast=16.0, slow=2.0)))
     par = dict(left=dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, conv=3, scale=hd ** -0.5, mask=dict(size=1000)),
                right=dict(heads=rh, dim=hd, vdim=hd, gate_cap=15.0))
     moe = dict(kind="moe", expert=dict(ff=ff // 4, limit=7.0), router=dict(experts=16, top=4, groups=dict(count=4, keep=2)))
@@ -292,7 +292,7 @@ def tamovik_config(width, ff, nh, nkv, hd, rh, runs, vocab):
         mlp = dict(kind="dense", ff=ff) if i == 0 else moe
         layers.append(dict(type="parallel", mixer=par, mlp=mlp) if i % 3 == 1 else dict(type="latent_attention", mixer=lat, mlp=mlp))
     return dict(architecture="Tamovik", vocab=vocab, width=width, norm=dict(eps=1e-5),
-                embedding=dict(bigram=dict(buckets=vocab - 1, mul_prev=31, mul_cur=17)), layers=layers)
+                embedding=dict(bigram=dict(buckets=vocab - 1, mul_prev=8191, mul_cur=131)), layers=layers)
 
 
 def arch_points(torch, a):

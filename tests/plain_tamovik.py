@@ -78,15 +78,16 @@ def stretched_frequencies(rot):
     return out, 0.1 * math.log(sc["factor"]) + 1.0
 
 
-def rotate_half(v, pos, rot):
+def rotate_half(v, pos, rot, angle_dtype=torch.float32):
     """``v [..., n]`` at position ``pos`` (a number, or one position per row of ``v [T, n]``): the first ``rot.dims``
-    elements rotated, element i with i + dims/2."""
+    elements rotated, element i with i + dims/2.  The design forms positions and angles in 32-bit (``angle_dtype``): the
+    frequency and the product ``pos * f_i`` are rounded to that type before the cosine and sine are taken."""
     if not rot:
         return v
     dims = rot["dims"]
     f, mag = stretched_frequencies(rot)
     half = dims // 2
-    a = torch.as_tensor(pos, dtype=F)[..., None] * torch.tensor(f, dtype=F)          # [..., half]
+    a = (torch.as_tensor(pos, dtype=angle_dtype)[..., None] * torch.tensor(f, dtype=angle_dtype)).to(F)          # [..., half]
     c, s = torch.cos(a) * mag, torch.sin(a) * mag
     u, w = v[..., :half], v[..., half:dims]
     return torch.cat([u * c - w * s, w * c + u * s, v[..., dims:]], dim=-1)

@@ -126,9 +126,11 @@ def test_rotation_keeps_relative_angles_and_scales_by_its_factor():
     assert mag == pytest.approx(0.1 * math.log(4.0) + 1.0)
     assert f[0] == pytest.approx(plain_f[0]) and f[-1] == pytest.approx(plain_f[-1] / 4.0)       # fast pairs stay, slow ones stretch
     a, b = torch.randn(12, generator=g).double(), torch.randn(12, generator=g).double()
-    d1 = PT.rotate_half(a, 7, rot) @ PT.rotate_half(b, 3, rot)
-    d2 = PT.rotate_half(a, 107, rot) @ PT.rotate_half(b, 103, rot)
+    d1 = PT.rotate_half(a, 7, rot, F) @ PT.rotate_half(b, 3, rot, F)
+    d2 = PT.rotate_half(a, 107, rot, F) @ PT.rotate_half(b, 103, rot, F)
     assert float(d1) == pytest.approx(float(d2), abs=1e-9)
+    d3 = PT.rotate_half(a, 107, rot) @ PT.rotate_half(b, 103, rot)                  # angles rounded to 32 bits, as the design has them
+    assert float(d3) == pytest.approx(float(d1), abs=1e-4) and float(d3) != float(d2)
     assert float(PT.rotate_half(a, 5, rot)[:8].norm()) == pytest.approx(mag * float(a[:8].norm()))
     assert torch.equal(PT.rotate_half(a, 5, rot)[8:], a[8:])
 

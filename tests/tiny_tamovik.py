@@ -64,12 +64,12 @@ TB_INIT = dict(seed=9, std_matrix=0.1, std_embedding=0.7, std_gain=0.15, std_bia
 # sizes the fast bfloat16 products and the tensor-core attention kernels take: attention heads of 64 with chunks of 100,
 # latent heads whose dim + rot_dim equals vdim (64 and 128), so that whole prompts of 256 tokens and more run over
 # per-head keys and values; memory heads of 64 x 32
-TF = _cfg(256, 128, 1e-5, 509, 31, 17,
-          [_lat(4, 32, 32, 64, 64, 0.11, (32, 2.0e5, 2.0, 128, 32.0, 1.0), _dense(256)),
-           _par(4, 2, 64, 3, 0.12, 100, 2, 64, 32, 10.0, _moe(64, 1.5, 8, 2, (4, 2))),
-           _lat(2, 96, 32, 128, 64, 0.09, (32, 3.0e5), _moe(64, 1.5, 8, 2, (2, 1))),
+TF = _cfg(256, 128, 1e-5, 251, 13, 7,
+          [_lat(4, 32, 32, 64, 64, 0.11, (32, 2.0e5, 3.0, 128, 16.0, 2.0), _dense(256)),
+           _par(4, 2, 64, 3, 0.12, 100, 2, 64, 32, 10.0, _moe(64, 1.75, 8, 2, (4, 2))),
+           _lat(2, 96, 32, 128, 64, 0.09, (32, 3.0e5), _moe(64, 2.5, 8, 2, (2, 1))),
            _par(2, 2, 128, 3, 0.09, 200, 4, 32, 64, 8.0, _moe(96, 1.25, 4, 3)),
-           _par(8, 2, 32, 2, 0.18, None, 2, 32, 32, 15.0, _dense(128))])
+           _par(8, 2, 32, 2, 0.18, None, 2, 32, 32, 14.0, _dense(128))])
 TF_INIT = dict(seed=13, std_matrix=0.08, std_embedding=0.4, std_gain=0.1, std_bias=0.3)
 
 # attention WITHOUT chunks at head sizes 128 and 64 (the library's plain attention kernels: tcgen05 for prompts, pages by
