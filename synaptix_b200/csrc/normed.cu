@@ -2,7 +2,8 @@
 // and norms 32-bit.  One block a row (256 threads, or up to 1,024 where the rows are few); the row stays in shared memory
 // between its passes.
 //
-//   add_normed:   v   = a                                        (one term without a gain), or
+//   add_normed:   v   = a                                        (one term without a gain; or, with `place`: the weighted
+//                       sum of rows of a, sum_k wts[t, k] a[place[t, k]], a mixture of experts' chosen results), or
 //                 v   = f * (rms_norm(a) ga + rms_norm(b) gb)     (one or two terms with gains: mixers side by side)
 //                 d   = gp ? rms_norm(v) gp : v                   (the branch's own norm)
 //                 acc = h ? h[t] + d : d;   if write_h: h[t] = acc
@@ -57,7 +58,8 @@ template <typename TO, int W>
 __global__ void __launch_bounds__(1024) add_normed_kernel(
     float* __restrict__ h, const void* __restrict__ a, int a_dt, const float* __restrict__ ga,
     const void* __restrict__ b, int b_dt, const float* __restrict__ gb, float factor, const float* __restrict__ gp,
-    const float* __restrict__ go, float eps, TO* __restrict__ y, const int* __restrict__ rows, int H, int write_h) {
+    const float* __restrict__ go, float eps, TO* __restrict__ y, const int* __restrict__ rows, int H, int write_h,
+    const int* __restrict__ place, const float* __restrict__ wts, int top) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[33];
   pdl_wait();
@@ -74,7 +76,18 @@ __global__ void __launch_bounds__(1024) add_normed_kernel(
     for (int i = tid; i < H; i += NT) stfv<W>(row, i, v);
   } else if (ga == nullptr) {
     for (int i = tid; i < H; i += NT) {
-      ldv<W>(a, a_dt, base + i, v);
+      if (place) {                 // the branch is a weighted sum of rows of a (float32), the terms in their order
+#pragma unroll
+        for (int j = 0; j < W; ++j) v[j] = 0.f;
+        for (int k = 0; k < top; ++k) {
+          const float wk = wts[(size_t)t * top + k];
+          ldfv<W>((const float*)a, (size_t)place[(size_t)t * top + k] * H + i, u);
+#pragma unroll
+          for (int j = 0; j < W; ++j) v[j] = fmaf(wk, u[j], v[j]);
+        }
+      } else {
+        ldv<W>(a, a_dt, base + i, v);
+      }
       stfv<W>(row, i, v);
 #pragma unroll
       for (int j = 0; j < W; ++j) ssv += v[j] * v[j];
@@ -154,7 +167,7 @@ __global__ void __launch_bounds__(1024) add_normed_kernel(
 template <typename TO, int W>
 static int add_normed_launch(float* h, const void* a, int a_dt, const float* ga, const void* b, int b_dt, const float* gb,
                              float factor, const float* gp, const float* go, float eps, void* y, const int* rows, int R, int H,
-                             int write_h, cudaStream_t stream) {
+                             int write_h, const int* place, const float* wts, int top, cudaStream_t stream) {
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<TO, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   // few rows (single-token steps): a thread an element or a handful, so that each pass is one trip to memory; many rows:
@@ -162,19 +175,20 @@ static int add_normed_launch(float* h, const void* a, int a_dt, const float* ga,
   const int per = (H / W + 31) / 32 * 32;
   const int nt = R <= 296 ? (per > 1024 ? 1024 : (per < 128 ? 128 : per)) : 256;
   return sx_launch(add_normed_kernel<TO, W>, dim3(R), dim3(nt), smem, stream, h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps,
-                   (TO*)y, rows, H, write_h);
+                   (TO*)y, rows, H, write_h, place, wts, top);
 }
 
 extern "C" int sx_add_normed(float* h, const void* a, int a_dt, const float* ga, const void* b, int b_dt, const float* gb,
                              float factor, const float* gp, const float* go, float eps, void* y, int y_dt, const int* rows,
-                             int R, int H, int write_h, cudaStream_t stream) {
+                             int R, int H, int write_h, const int* place, const float* wts, int top, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (H <= 0 || (b != nullptr && (a == nullptr || ga == nullptr || gb == nullptr))) return SX_ERR_SIZE;
+  if (place != nullptr && (a == nullptr || a_dt != SX_F32 || ga != nullptr || wts == nullptr || top <= 0)) return SX_ERR_SIZE;
   if ((size_t)H * sizeof(float) > 200 * 1024) return SX_ERR_SIZE;
   const uintptr_t all = (uintptr_t)h | (uintptr_t)a | (uintptr_t)ga | (uintptr_t)b | (uintptr_t)gb | (uintptr_t)gp | (uintptr_t)go |
                         (uintptr_t)y;
   const bool v4 = (H % 4 == 0) && (all % 16 == 0);
-#define AN_GO(TO, W) return add_normed_launch<TO, W>(h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps, y, rows, R, H, write_h, stream)
+#define AN_GO(TO, W) return add_normed_launch<TO, W>(h, a, a_dt, ga, b, b_dt, gb, factor, gp, go, eps, y, rows, R, H, write_h, place, wts, top, stream)
   if (y == nullptr || y_dt == SX_F32) { if (v4) AN_GO(float, 4); AN_GO(float, 1); }
   if (y_dt == SX_BF16) { if (v4) AN_GO(bf16, 4); AN_GO(bf16, 1); }
 #undef AN_GO

@@ -25,7 +25,7 @@ from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, e
 from .sequence import add_rmsnorm_conv, capped_glu, mingru, retention, stream_add
 from .block import add_scaled, add_scaled_rmsnorm, scale_rows
 from .layernorm import add_layernorm
-from .normed import add_normed, embed_bigram
+from .normed import WeightedRows, add_normed, embed_bigram
 from .convqk import convqk_prepare, sigmoid_gate
 from .scored import attn_scored as attn_scored_all_heads, heads_prepare
 from .latent import (head_gate, latent_attention, latent_expand, latent_gather, latent_output, latent_prepare, latent_query,
@@ -38,7 +38,7 @@ __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavail
            "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
            "linear_into_residual", "linear_scaled", "projection_prepares_heads", "project_and_prepare", "rope_table",
            "add_rmsnorm_conv", "capped_glu", "mingru", "retention", "stream_add", "gate_activation",
-           "add_normed", "embed_bigram", "convqk_prepare", "sigmoid_gate", "add_scaled", "add_scaled_rmsnorm", "scale_rows", "add_layernorm", "attn_scored", "heads_prepare", "latent_attention", "latent_output", "latent_prepare",
+           "add_normed", "WeightedRows", "embed_bigram", "convqk_prepare", "sigmoid_gate", "add_scaled", "add_scaled_rmsnorm", "scale_rows", "add_layernorm", "attn_scored", "heads_prepare", "latent_attention", "latent_output", "latent_prepare",
            "latent_query", "latent_gather", "latent_expand", "latent_rotate_q", "head_gate", "mlstm", "ExpertPlan", "moe_combine", "moe_down", "moe_gate_up", "moe_route", "moe_sort"]
 
 

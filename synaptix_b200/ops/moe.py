@@ -118,11 +118,15 @@ def moe_down(z: torch.Tensor, down: torch.Tensor, plan: ExpertPlan) -> torch.Ten
 
 def moe_combine(y: torch.Tensor, plan: ExpertPlan, weights: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """``out[t] = sum_j weights[t, j] * y[place[t * top + j]]`` with the choices in their order; ``[T, width]``."""
-    require_cuda(y, weights)
+    return moe_combine_rows(y, plan.place, weights, out_dtype)
+
+
+def moe_combine_rows(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    require_cuda(y, weights, place)
     T, top = weights.shape
     if y.shape[0] != T * top or weights.dtype != torch.float32:
         raise KernelError("moe_combine: sizes do not fit")
     out = torch.empty((T, y.shape[1]), dtype=out_dtype, device=y.device)
-    check(fn("moe", "sx_moe_combine")(ptr(y), c_int(dt_code(y.dtype)), ptr(plan.place), ptr(weights), ptr(out),
+    check(fn("moe", "sx_moe_combine")(ptr(y), c_int(dt_code(y.dtype)), ptr(place), ptr(weights), ptr(out),
                                       c_int(dt_code(out_dtype)), c_int(T), c_int(y.shape[1]), c_int(top), stream()), "moe_combine")
     return out

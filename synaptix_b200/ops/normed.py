@@ -9,13 +9,36 @@ import torch
 from ._lib import KernelError, c_float, c_int, check, dt_code, fn, ptr, require_cuda, stream
 
 
+class WeightedRows:
+    """A branch that is a weighted sum of rows not formed yet: ``out[t] = sum_k weights[t, k] * rows[place[t * top + k]]``
+    (``rows`` float32 ``[T * top, width]``, ``place`` int32 ``[T * top]``, ``weights`` float32 ``[T, top]``): what a mixture
+    of experts holds before its last kernel.  ``add_normed`` takes it as its raw term and forms the sum on its way;
+    ``materialize()`` runs the mixture's own kernel (``moe_combine``) and gives the tensor in ``dtype``."""
+    __slots__ = ("rows", "place", "weights", "dtype", "_sum")
+
+    def __init__(self, rows, place, weights, dtype):
+        self.rows, self.place, self.weights, self.dtype = rows, place, weights, dtype
+        self._sum = None
+
+    @property
+    def shape(self):
+        return (self.weights.shape[0], self.rows.shape[1])
+
+    def materialize(self) -> torch.Tensor:
+        if self._sum is None:
+            from .moe import moe_combine_rows
+            self._sum = moe_combine_rows(self.rows, self.place, self.weights, self.dtype)
+        return self._sum
+
+
 def add_normed(h: Optional[torch.Tensor], terms: Sequence, post_gain: Optional[torch.Tensor], eps: float,
                out_dtype: Optional[torch.dtype], *, factor: float = 1.0, out_gain: Optional[torch.Tensor] = None,
-               rows: Optional[torch.Tensor] = None, width: Optional[int] = None) -> Optional[torch.Tensor]:
+               rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """One pass per row over a branch on its way into the residual stream ``h`` (float32 ``[T, width]``, summed into in
     place unless ``rows`` is given; ``None``: there is no stream and the result is the branch alone).
 
-    ``terms``: none (nothing is added), one ``(x, None)`` (the branch is ``x``), or one or two ``(x_i, gain_i)``: the
+    ``terms``: none (nothing is added), one ``(x, None)`` (the branch is ``x``; ``x`` may be a ``WeightedRows``, the
+    weighted sum of rows that a mixture of experts hands on), or one or two ``(x_i, gain_i)``: the
     branch is ``factor * sum_i rms_norm(x_i) * gain_i`` (mixers side by side, each with a norm of its own).  With
     ``post_gain`` the branch is normed once more, ``rms_norm(branch) * post_gain``, before it is added.  Returned: the
     rows after the sum in ``out_dtype`` (what the next sublayer reads), or ``rms_norm`` of them times ``out_gain``; all
@@ -24,14 +47,26 @@ def add_normed(h: Optional[torch.Tensor], terms: Sequence, post_gain: Optional[t
     if len(terms) > 2 or (len(terms) == 2 and any(g is None for _, g in terms)):
         raise KernelError("add_normed: one raw term, or one or two terms with gains")
     (a, ga), (b, gb) = (terms + [(None, None), (None, None)])[:2]
-    require_cuda(h, a, ga, b, gb, post_gain, out_gain, rows)
-    ref = h if h is not None else a
-    if ref is None:
+    place = wts = None
+    top = 0
+    if isinstance(a, WeightedRows):
+        if ga is not None or b is not None:
+            raise KernelError("add_normed: a weighted sum of rows is a raw term and stands alone")
+        place, wts, top, a_shape = a.place, a.weights, a.weights.shape[1], a.shape
+        a = a.rows
+        if a.dtype != torch.float32:
+            raise KernelError("add_normed: the rows of a weighted sum are float32")
+    else:
+        a_shape = None if a is None else tuple(a.shape)
+    require_cuda(h, a, ga, b, gb, post_gain, out_gain, rows, place, wts)
+    if h is None and a is None:
         raise KernelError("add_normed: neither a stream nor a branch")
-    T, H = ref.shape
-    for t in (a, b):
-        if t is not None and tuple(t.shape) != (T, H):
-            raise KernelError("add_normed: a branch must have the stream's shape")
+    T, H = h.shape if h is not None else a_shape
+    if a_shape is not None and tuple(a_shape) != (T, H):
+        raise KernelError("add_normed: a branch must have the stream's shape")
+    ref = h if h is not None else a
+    if b is not None and tuple(b.shape) != (T, H):
+        raise KernelError("add_normed: a branch must have the stream's shape")
     for g in (ga, gb, post_gain, out_gain):
         if g is not None and (g.dtype != torch.float32 or g.numel() != H):
             raise KernelError("add_normed: gains are float32 vectors over the width")
@@ -43,7 +78,7 @@ def add_normed(h: Optional[torch.Tensor], terms: Sequence, post_gain: Optional[t
         ptr(h), ptr(a), c_int(dt_code(a.dtype) if a is not None else 0), ptr(ga), ptr(b),
         c_int(dt_code(b.dtype) if b is not None else 0), ptr(gb), c_float(factor), ptr(post_gain), ptr(out_gain), c_float(eps),
         ptr(y), c_int(dt_code(out_dtype) if out_dtype is not None else 0), ptr(rows), c_int(R), c_int(H),
-        c_int(1 if (rows is None and h is not None) else 0), stream()), "add_normed")
+        c_int(1 if (rows is None and h is not None) else 0), ptr(place), ptr(wts), c_int(top), stream()), "add_normed")
     return y
 
 

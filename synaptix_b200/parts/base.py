@@ -146,7 +146,7 @@ class PendingLinear:
 
 def plain(t):
     """``t`` as a tensor, whatever deferred form it came in."""
-    return t.materialize() if isinstance(t, (PendingLinear, PendingNorm, ScaledRows, ScaledSum, NormedDelta, NormedSum)) else t
+    return t.materialize() if hasattr(t, "materialize") else t
 
 
 class NormedSum:
@@ -183,7 +183,7 @@ class NormedDelta:
     ``mult * norm(x + bias)`` as one float32 tensor.
 
     ``norm`` may also be an RMS norm (it has no ``bias`` vector; ``mult`` is then 1 and there is no product bias), and
-    ``x`` may then be a ``NormedSum``."""
+    ``x`` may then be a ``NormedSum`` or a mixture of experts' ``WeightedRows``."""
     __slots__ = ("x", "norm", "mult", "bias", "_sum")
 
     def __init__(self, x, norm, mult: float = 1.0, bias=None):
@@ -204,6 +204,9 @@ class NormedDelta:
         """``(terms, factor)`` as ``ops.add_normed`` takes them."""
         if isinstance(self.x, NormedSum):
             return self.x.terms, self.x.factor
+        from ..ops import WeightedRows
+        if isinstance(self.x, WeightedRows):          # a mixture's weighted sum, formed inside the kernel
+            return [(self.x, None)], 1.0
         return [(plain(self.x), None)], 1.0
 
     def materialize(self) -> torch.Tensor:

@@ -317,4 +317,6 @@ class PostNormBlock(Part):
         if self.ffn is None:
             return h, a
         y = self._read(h, a, dtype)
+        if getattr(self.ffn, "can_defer_combine", False):
+            return h, NormedDelta(self.ffn.forward(y, ctx, defer_combine=True), self.norm2)
         return h, NormedDelta(self.ffn.forward(y, ctx), self.norm2)

@@ -134,7 +134,9 @@ class MixtureOfExperts(FeedForward):
         self.gate_up = to_device_matrix(torch.stack(gu), rt)
         self.down = to_device_matrix(torch.stack([tensors[self._name(e, "down")] for e in range(self.experts)]), rt)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    can_defer_combine = True        # forward(..., defer_combine=True) may hand the weighted sum on unformed (WeightedRows)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, defer_combine: bool = False) -> torch.Tensor:
         ids, weights = ops.moe_route(x, self.router, self.top, self.scale, self.SUM_EPS, scoring=self.scoring,
                                      correction=self.correction, groups=self.groups, renormalize=self.renormalize)
         plan = ops.moe_sort(ids, self.experts)
@@ -144,4 +146,6 @@ class MixtureOfExperts(FeedForward):
         else:
             z = ops.moe_gate_up(x, self.gate_up, plan, self.top)
         y = ops.moe_down(z, self.down, plan)
+        if defer_combine:           # a block that norms this branch on its way into the stream forms the sum there
+            return ops.WeightedRows(y, plan.place, weights, x.dtype)
         return ops.moe_combine(y, plan, weights, x.dtype)

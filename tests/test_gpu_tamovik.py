@@ -111,6 +111,20 @@ def test_branch_normed_on_its_way_into_the_stream(width, dtype):
     hd = h.cuda()
     y = ops.add_normed(hd, [], None, 0.0, DT[dtype])
     assert torch.equal(hd.cpu(), h) and torch.equal(y.cpu(), h.to(DT[dtype]))
+    # the branch as a weighted sum of rows that is formed on the way (what a mixture of experts hands on)
+    top = 3
+    rows_y = torch.randn(T * top, width, generator=g)
+    place = torch.randperm(T * top, generator=g).to(torch.int32)
+    wts = torch.rand(T, top, generator=g)
+    mix = torch.stack([sum(wts[t, k].double() * rows_y[int(place[t * top + k])].double() for k in range(top)) for t in range(T)])
+    wr = ops.WeightedRows(rows_y.cuda(), place.cuda(), wts.cuda(), DT[dtype])
+    assert torch.allclose(wr.materialize().float().cpu().double(), mix, **tol)
+    ref_h = h.double() + PT.rms_norm(mix, gp, eps)
+    hd = h.cuda()
+    y = ops.add_normed(hd, [(wr, None)], gp.cuda(), eps, DT[dtype])
+    assert torch.allclose(hd.cpu().double(), ref_h, atol=2e-5) and torch.allclose(y.float().cpu().double(), ref_h, **tol)
+    y = ops.add_normed(h.cuda(), [(wr, None)], gp.cuda(), eps, DT[dtype], out_gain=go.cuda(), rows=i32(rows))
+    assert torch.allclose(y.float().cpu().double(), PT.rms_norm(ref_h, go, eps)[rows], **tol)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
